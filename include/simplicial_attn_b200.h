@@ -1,0 +1,102 @@
+/* C ABI of the B200 2-simplicial attention library (libsimplicial_attn_b200.so).
+ *
+ * The operator:  logits_ijk = scale * sum_d Q_id * K1_jd * (K2_kd + k2_bias)
+ *                over the causal windows  j in (i-w1, i],  k in (i-w2, i];
+ *                P = softmax over each query's (j,k) pairs;
+ *                O_i = sum_jk P_ijk * V1_j * (V2_k + v2_bias);   LSE_i = log sum_jk exp(logits_ijk).
+ *
+ * Every entry point takes plain pointers and sizes, allocates nothing, launches on the caller's
+ * stream, never synchronises the host (except sa_read_status) and returns an sa_status.
+ * All buffers -- inputs, outputs, LSE and workspace -- are owned by the caller and live in device
+ * memory of the current CUDA device.
+ *
+ * Logical tensor shapes (the reference's, simplicial/reference.py:16-18): Q, O, dO, dQ are
+ * [B, N, H, D]; K1, V1, dK1, dV1 are [B, N + halo1, Hkv, D]; K2, V2, dK2, dV2 are
+ * [B, N + halo2, Hkv, D]; LSE is [B, H, N] fp32 contiguous.  Any (b, n, h) element strides are
+ * accepted, the d stride is 1.  H % Hkv == 0 and query head h reads KV head h / (H / Hkv).
+ * halo1/halo2 count extra leading K/V rows that precede query row 0 (a sequence shard's halo);
+ * query row n pairs with K1 row n + halo1 and K2 row n + halo2; windows are clipped at row 0.
+ */
+#ifndef SIMPLICIAL_ATTN_B200_H
+#define SIMPLICIAL_ATTN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    SA_OK = 0,
+    SA_ERR_NULL_POINTER = 1,     /* a required pointer is NULL */
+    SA_ERR_BAD_SHAPE = 2,        /* non-positive extent, H % Hkv != 0, negative halo, window < 1 */
+    SA_ERR_BAD_STRIDE = 3,       /* a stride breaks the 16-byte alignment the kernels need */
+    SA_ERR_UNSUPPORTED = 4,      /* dtype / head dim / window outside what the chosen kernel handles */
+    SA_ERR_WORKSPACE = 5,        /* workspace too small or misaligned (256 bytes) */
+    SA_ERR_LAUNCH = 6,           /* CUDA reported an error at launch */
+    SA_ERR_DEVICE_TIMEOUT = 7,   /* a bounded device-side wait gave up (seen through sa_read_status) */
+    SA_ERR_NOT_SM100 = 8         /* the current device is not compute capability 10.x */
+} sa_status;
+
+typedef enum { SA_BF16 = 0, SA_F16 = 1, SA_F32 = 2 } sa_dtype;
+
+/* Kernel family.  AUTO picks the tcgen05 kernels whenever they cover the problem (bf16, D in
+ * {64,128}, effective w2 <= 128) and the general kernels otherwise.  The general kernels are plain
+ * CUDA-core fp32 code for every dtype, head dim and window; they also serve as the on-device
+ * cross-check of the tensor-core kernels. */
+typedef enum { SA_ALGO_AUTO = 0, SA_ALGO_GENERAL = 1, SA_ALGO_TCGEN05 = 2 } sa_algo;
+
+/* (b, n, h) element strides of one tensor; the innermost (d) stride is 1. */
+typedef struct { int64_t b, n, h; } sa_strides;
+
+typedef struct {
+    int32_t B, N, H, Hkv, D;
+    int32_t w1, w2;              /* window sizes, >= 1 (values above the row count are clipped) */
+    int32_t halo1, halo2;        /* leading halo rows of K1/V1 and of K2/V2 */
+    int32_t dtype;               /* sa_dtype of every tensor except LSE */
+    int32_t algo;                /* sa_algo */
+    float scale, k2_bias, v2_bias;
+    sa_strides q, k1, k2, v1, v2, o;          /* forward tensors (o also describes O in backward) */
+    sa_strides d_o, dq, dk1, dk2, dv1, dv2;   /* backward tensors (ignored by sa_forward) */
+} sa_params;
+
+/* Replaces the launch of two_simplicial_attn_fwd_kernel in
+ * TwoSimplicialAttentionFunction.forward (simplicial/triton_impl.py:19-58; kernel
+ * simplicial/kernels.py:11-171).  Writes O (dtype) and LSE (fp32, natural log; the reference's
+ * `M`, simplicial/kernels.py:164-167).  `workspace` must hold sa_forward_workspace_size() bytes,
+ * 256-byte aligned. */
+int sa_forward(const sa_params* p, const void* q, const void* k1, const void* k2, const void* v1,
+               const void* v2, void* o, float* lse, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Replaces compute_D_kernel plus the two backward launches of
+ * TwoSimplicialAttentionFunction.backward (simplicial/triton_impl.py:61-158; kernels
+ * simplicial/kernels.py:175-382, :386-566, :569-571).  Any of dq, dk1, dk2, dv1, dv2 may be NULL
+ * (gradient not needed, the reference's needs_input_grad gating, triton_impl.py:73-77).  Outputs
+ * are overwritten, not accumulated into, and are written without atomics in a fixed order. */
+int sa_backward(const sa_params* p, const void* q, const void* k1, const void* k2, const void* v1,
+                const void* v2, const void* o, const float* lse, const void* d_o, void* dq, void* dk1,
+                void* dk2, void* dv1, void* dv2, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Workspace sizes in bytes for the given problem (the reference allocates its work buffers inside
+ * the autograd function, triton_impl.py:23-25,73-77; here the caller does).  Never 0: the first
+ * 256 bytes hold the device status word. */
+size_t sa_forward_workspace_size(const sa_params* p);
+size_t sa_backward_workspace_size(const sa_params* p);
+
+/* Synchronises `stream` and returns the status word the kernels of earlier calls left in
+ * `workspace` (SA_OK or SA_ERR_DEVICE_TIMEOUT), then clears it.  The reference has no
+ * counterpart: its failures surface as Triton exceptions. */
+int sa_read_status(void* workspace, void* stream);
+
+/* Which kernel family AUTO resolves to for `p` (SA_ALGO_GENERAL or SA_ALGO_TCGEN05), or a negative
+ * sa_status if `p` is invalid. */
+int sa_resolve_algo(const sa_params* p);
+
+const char* sa_strerror(int status);
+int sa_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SIMPLICIAL_ATTN_B200_H */
