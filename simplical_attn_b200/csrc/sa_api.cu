@@ -1,0 +1,268 @@
+// C ABI of libsimplicial_attn_b200.so: argument validation, kernel selection and launches.
+// Declarations and the reference interfaces they replace: include/simplicial_attn_b200.h.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
+#include "sa_common.cuh"
+#include "sa_general.cuh"
+#include "sa_tc_bwd.cuh"
+#include "sa_tc_fwd.cuh"
+
+namespace {
+
+using sa::KParams;
+
+constexpr size_t kStatusBytes = 256;
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+bool stride_ok8(const sa_strides& s) { return s.b % 8 == 0 && s.n % 8 == 0 && s.h % 8 == 0; }
+
+int elem_size(int dtype) { return dtype == SA_F32 ? 4 : 2; }
+
+int validate(const sa_params* p) {
+    if (!p) return SA_ERR_NULL_POINTER;
+    if (p->B < 1 || p->N < 1 || p->H < 1 || p->Hkv < 1 || p->D < 1) return SA_ERR_BAD_SHAPE;
+    if (p->H % p->Hkv != 0 || p->w1 < 1 || p->w2 < 1 || p->halo1 < 0 || p->halo2 < 0) return SA_ERR_BAD_SHAPE;
+    if (p->dtype < SA_BF16 || p->dtype > SA_F32) return SA_ERR_UNSUPPORTED;
+    if (p->D > 256) return SA_ERR_UNSUPPORTED;
+    if (p->algo < SA_ALGO_AUTO || p->algo > SA_ALGO_TCGEN05) return SA_ERR_UNSUPPORTED;
+    return SA_OK;
+}
+
+KParams make_kparams(const sa_params* p) {
+    KParams k{};
+    k.B = p->B; k.N = p->N; k.H = p->H; k.Hkv = p->Hkv; k.D = p->D; k.G = p->H / p->Hkv;
+    k.halo1 = p->halo1; k.halo2 = p->halo2;
+    k.n1 = p->N + p->halo1; k.n2 = p->N + p->halo2;
+    k.w1 = p->w1 < k.n1 ? p->w1 : k.n1;
+    k.w2 = p->w2 < k.n2 ? p->w2 : k.n2;
+    k.scale = p->scale; k.k2_bias = p->k2_bias; k.v2_bias = p->v2_bias;
+    k.q = p->q; k.k1 = p->k1; k.k2 = p->k2; k.v1 = p->v1; k.v2 = p->v2; k.o = p->o;
+    k.d_o = p->d_o; k.dq = p->dq; k.dk1 = p->dk1; k.dk2 = p->dk2; k.dv1 = p->dv1; k.dv2 = p->dv2;
+    return k;
+}
+
+// Whether the tensor-core kernels cover the problem's shape and dtype (pointer alignment is
+// checked at the call).
+bool tc_shape_ok(const sa_params* p, bool backward) {
+    const KParams k = make_kparams(p);
+    if (p->dtype != SA_BF16) return false;
+    if (p->D != 64 && p->D != 128) return false;
+    if (k.w2 > 128) return false;
+    if (p->scale <= 0.f) return false;            // the row maximum is taken before scaling
+    if (!stride_ok8(p->q) || !stride_ok8(p->k1) || !stride_ok8(p->k2) || !stride_ok8(p->v1) || !stride_ok8(p->v2) ||
+        !stride_ok8(p->o))
+        return false;
+    if (backward && (!stride_ok8(p->d_o) || !stride_ok8(p->dq) || !stride_ok8(p->dk1) || !stride_ok8(p->dk2) ||
+                     !stride_ok8(p->dv1) || !stride_ok8(p->dv2)))
+        return false;
+    return true;
+}
+
+int dw_log2_of(int w2) {
+    int l = 0;
+    while ((1 << l) < w2) ++l;
+    return l;
+}
+
+// ---- driver entry point for tensor-map encoding (resolved at run time; no link against libcuda)
+PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    });
+    return fn;
+}
+
+// Tensor map over a bf16 [B, rows, heads, D] tensor with (b, n, h) element strides; a box is 64
+// elements of one row by `box_rows` rows, landing 128-byte swizzled.
+bool make_map(CUtensorMap* map, const void* base, int B, int rows, int heads, int D, const sa_strides& st, int box_rows) {
+    auto enc = get_encode();
+    if (!enc) return false;
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)heads, (cuuint64_t)B};
+    // A stride of an extent-1 dimension is never used to form an address; give it a harmless value.
+    auto sb = [&](int64_t s, int extent) { return (cuuint64_t)((extent > 1 ? s : (int64_t)D) * 2); };
+    cuuint64_t strides[3] = {sb(st.n, rows), sb(st.h, heads), sb(st.b, B)};
+    cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+struct DeviceInfo {
+    int sm_count = 0;
+    int cc_major = 0;
+    bool attrs_set = false;
+};
+
+DeviceInfo& device_info() {
+    static DeviceInfo info[64];
+    static std::mutex mu;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lock(mu);
+    DeviceInfo& d = info[dev & 63];
+    if (d.sm_count == 0) {
+        cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    }
+    return d;
+}
+
+template <typename Kern>
+bool set_smem(Kern kern, int bytes) {
+    return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+}
+
+int launch_fwd_tc(const sa_params* p, const KParams& k, const void* q, const void* k1, const void* k2, const void* v1,
+                  const void* v2, void* o, float* lse, void* workspace, cudaStream_t st) {
+    DeviceInfo& dev = device_info();
+    if (dev.cc_major != 10) return SA_ERR_NOT_SM100;
+    CUtensorMap map_k1, map_v1;
+    if (!make_map(&map_k1, k1, k.B, k.n1, k.Hkv, k.D, k.k1, sa::tc::kColTile)) return SA_ERR_BAD_STRIDE;
+    if (!make_map(&map_v1, v1, k.B, k.n1, k.Hkv, k.D, k.v1, sa::tc::kColTile)) return SA_ERR_BAD_STRIDE;
+    sa::tc::FwdTcParams P{};
+    P.k = k;
+    P.dw_log2 = dw_log2_of(k.w2);
+    const int qpb = (sa::tc::kNumRowTiles * sa::tc::kRowTile) >> P.dw_log2;
+    P.num_qblocks = (k.N + qpb - 1) / qpb;
+    P.num_units = (long)k.B * k.H * P.num_qblocks;
+    P.status = reinterpret_cast<sa::DeviceStatus*>(workspace);
+    const long grid = P.num_units < dev.sm_count ? P.num_units : dev.sm_count;
+    if (k.D == 128) {
+        using L = sa::tc::FwdSmem<128>;
+        auto kern = sa::tc::fwd_tc_kernel<128>;
+        if (!set_smem(kern, L::kAlloc)) return SA_ERR_LAUNCH;
+        kern<<<(unsigned)grid, sa::tc::kFwdThreads, L::kAlloc, st>>>(P, map_k1, map_v1, (const __nv_bfloat16*)q,
+                                                                      (const __nv_bfloat16*)k2, (const __nv_bfloat16*)v2,
+                                                                      (__nv_bfloat16*)o, lse);
+    } else {
+        using L = sa::tc::FwdSmem<64>;
+        auto kern = sa::tc::fwd_tc_kernel<64>;
+        if (!set_smem(kern, L::kAlloc)) return SA_ERR_LAUNCH;
+        kern<<<(unsigned)grid, sa::tc::kFwdThreads, L::kAlloc, st>>>(P, map_k1, map_v1, (const __nv_bfloat16*)q,
+                                                                      (const __nv_bfloat16*)k2, (const __nv_bfloat16*)v2,
+                                                                      (__nv_bfloat16*)o, lse);
+    }
+    (void)p;
+    return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
+}
+
+int resolve(const sa_params* p, bool backward) {
+    if (p->algo == SA_ALGO_GENERAL) return SA_ALGO_GENERAL;
+    const bool ok = tc_shape_ok(p, backward);
+    if (p->algo == SA_ALGO_TCGEN05) return ok ? SA_ALGO_TCGEN05 : -SA_ERR_UNSUPPORTED;
+    return ok ? SA_ALGO_TCGEN05 : SA_ALGO_GENERAL;
+}
+
+}  // namespace
+
+extern "C" {
+
+int sa_version(void) { return 100; }
+
+const char* sa_strerror(int status) {
+    switch (status) {
+        case SA_OK: return "ok";
+        case SA_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case SA_ERR_BAD_SHAPE: return "bad shape: extents must be positive, H % Hkv == 0, windows >= 1, halos >= 0";
+        case SA_ERR_BAD_STRIDE: return "bad stride or pointer alignment: the tensor-core kernels need 16-byte aligned rows";
+        case SA_ERR_UNSUPPORTED: return "unsupported dtype, head dim, window or kernel choice";
+        case SA_ERR_WORKSPACE: return "workspace too small or not 256-byte aligned";
+        case SA_ERR_LAUNCH: return "CUDA reported an error at kernel launch";
+        case SA_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait gave up";
+        case SA_ERR_NOT_SM100: return "the tensor-core kernels need a compute capability 10.x device";
+        default: return "unknown status";
+    }
+}
+
+int sa_resolve_algo(const sa_params* p) {
+    const int v = validate(p);
+    if (v != SA_OK) return -v;
+    return resolve(p, true);
+}
+
+size_t sa_forward_workspace_size(const sa_params* p) {
+    (void)p;
+    return kStatusBytes;
+}
+
+size_t sa_backward_workspace_size(const sa_params* p) {
+    if (validate(p) != SA_OK) return kStatusBytes;
+    if (resolve(p, true) != SA_ALGO_TCGEN05) return kStatusBytes;
+    return kStatusBytes + sa::tc::bwd_workspace_bytes(make_kparams(p));
+}
+
+int sa_read_status(void* workspace, void* stream) {
+    if (!workspace) return SA_ERR_NULL_POINTER;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    sa::DeviceStatus h{};
+    if (cudaMemcpyAsync(&h, workspace, sizeof(h), cudaMemcpyDeviceToHost, st) != cudaSuccess) return SA_ERR_LAUNCH;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return SA_ERR_LAUNCH;
+    if (h.code != 0) cudaMemsetAsync(workspace, 0, sizeof(h), st);
+    return h.code;
+}
+
+int sa_forward(const sa_params* p, const void* q, const void* k1, const void* k2, const void* v1, const void* v2, void* o,
+               float* lse, void* workspace, size_t workspace_bytes, void* stream) {
+    const int v = validate(p);
+    if (v != SA_OK) return v;
+    if (!q || !k1 || !k2 || !v1 || !v2 || !o || !lse || !workspace) return SA_ERR_NULL_POINTER;
+    if (workspace_bytes < sa_forward_workspace_size(p) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return SA_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const KParams k = make_kparams(p);
+    int algo = resolve(p, false);
+    if (algo < 0) return -algo;
+    if (algo == SA_ALGO_TCGEN05 &&
+        !(aligned16(q) && aligned16(k1) && aligned16(k2) && aligned16(v1) && aligned16(v2) && aligned16(o))) {
+        if (p->algo == SA_ALGO_TCGEN05) return SA_ERR_BAD_STRIDE;
+        algo = SA_ALGO_GENERAL;
+    }
+    if (algo == SA_ALGO_TCGEN05) return launch_fwd_tc(p, k, q, k1, k2, v1, v2, o, lse, workspace, st);
+    const cudaError_t e = sa::general::launch_fwd(p->dtype, k, q, k1, k2, v1, v2, o, lse, st);
+    (void)elem_size;
+    return e == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
+}
+
+int sa_backward(const sa_params* p, const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
+                const void* o, const float* lse, const void* d_o, void* dq, void* dk1, void* dk2, void* dv1, void* dv2,
+                void* workspace, size_t workspace_bytes, void* stream) {
+    const int v = validate(p);
+    if (v != SA_OK) return v;
+    if (!q || !k1 || !k2 || !v1 || !v2 || !o || !lse || !d_o || !workspace) return SA_ERR_NULL_POINTER;
+    if (workspace_bytes < sa_backward_workspace_size(p) || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+        return SA_ERR_WORKSPACE;
+    if (!dq && !dk1 && !dk2 && !dv1 && !dv2) return SA_OK;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const KParams k = make_kparams(p);
+    int algo = resolve(p, true);
+    if (algo < 0) return -algo;
+    auto al = [](const void* x) { return x == nullptr || aligned16(x); };
+    if (algo == SA_ALGO_TCGEN05 && !(aligned16(q) && aligned16(k1) && aligned16(k2) && aligned16(v1) && aligned16(v2) &&
+                                     aligned16(o) && aligned16(d_o) && al(dq) && al(dk1) && al(dk2) && al(dv1) && al(dv2))) {
+        if (p->algo == SA_ALGO_TCGEN05) return SA_ERR_BAD_STRIDE;
+        algo = SA_ALGO_GENERAL;
+    }
+    if (algo == SA_ALGO_TCGEN05) {
+        const int rc = sa::tc::launch_bwd(k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2,
+                                          static_cast<uint8_t*>(workspace) + kStatusBytes,
+                                          reinterpret_cast<sa::DeviceStatus*>(workspace), st);
+        if (rc != -1) return rc;      // -1: the tensor-core backward declines this problem
+        if (p->algo == SA_ALGO_TCGEN05) return SA_ERR_UNSUPPORTED;
+    }
+    const cudaError_t e = sa::general::launch_bwd(p->dtype, k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2, st);
+    return e == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
+}
+
+}  // extern "C"

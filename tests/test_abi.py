@@ -1,0 +1,85 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every symbol the header declares, and
+its argument validation and kernel selection work without a GPU (no compute is launched)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from simplical_attn_b200 import _abi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "simplicial_attn_b200.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sa_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_exported():
+    lib = _abi.load()
+    syms = declared_symbols()
+    assert set(_abi.EXPORTS) <= set(syms)
+    for s in syms:
+        assert hasattr(lib, s), s
+
+
+def test_struct_layout_matches_header():
+    # 11 int32 + 3 float + 12 x (3 x int64)
+    assert ctypes.sizeof(_abi.Params) == 11 * 4 + 3 * 4 + 12 * 24
+    assert _abi.Params.q.offset == 56
+
+
+def _params(**kw):
+    p = _abi.Params()
+    p.B, p.N, p.H, p.Hkv, p.D, p.w1, p.w2 = 1, 64, 4, 2, 128, 16, 8
+    p.dtype, p.algo, p.scale = _abi.SA_BF16, _abi.SA_ALGO_AUTO, 0.1
+    for name in ("q", "k1", "k2", "v1", "v2", "o", "d_o", "dq", "dk1", "dk2", "dv1", "dv2"):
+        setattr(p, name, _abi.Strides(64 * 4 * 128, 4 * 128, 128))
+    for k, v in kw.items():
+        setattr(p, k, v)
+    return p
+
+
+def test_validation_codes():
+    lib = _abi.load()
+    nul = ctypes.c_void_p(0)
+    args = [nul] * 8 + [0, nul]
+    assert lib.sa_forward(ctypes.byref(_params(H=3)), *args) == 2            # H % Hkv
+    assert lib.sa_forward(ctypes.byref(_params(w1=0)), *args) == 2
+    assert lib.sa_forward(ctypes.byref(_params(halo1=-1)), *args) == 2
+    assert lib.sa_forward(ctypes.byref(_params(D=512)), *args) == 4
+    assert lib.sa_forward(ctypes.byref(_params(dtype=7)), *args) == 4
+    assert lib.sa_forward(ctypes.byref(_params()), *args) == 1               # NULL pointers
+    assert "NULL" in _abi.strerror(1)
+    with pytest.raises(_abi.SimplicialAttnError):
+        _abi.check("sa_forward", 2)
+
+
+def test_kernel_selection():
+    lib = _abi.load()
+    r = lambda **kw: lib.sa_resolve_algo(ctypes.byref(_params(**kw)))
+    assert r() == _abi.SA_ALGO_TCGEN05
+    assert r(D=64) == _abi.SA_ALGO_TCGEN05
+    assert r(D=32) == _abi.SA_ALGO_GENERAL
+    assert r(dtype=_abi.SA_F32) == _abi.SA_ALGO_GENERAL
+    assert r(w2=200, N=4096) == _abi.SA_ALGO_GENERAL
+    assert r(w2=200, N=64) == _abi.SA_ALGO_TCGEN05                           # window clipped to 64 rows
+    assert r(algo=_abi.SA_ALGO_GENERAL) == _abi.SA_ALGO_GENERAL
+    assert r(D=32, algo=_abi.SA_ALGO_TCGEN05) == -4
+    assert r(q=_abi.Strides(1000, 100, 4)) == _abi.SA_ALGO_GENERAL           # rows not 16-byte aligned
+    assert r(H=5) == -2
+    assert lib.sa_forward_workspace_size(ctypes.byref(_params())) >= 256
+    assert lib.sa_backward_workspace_size(ctypes.byref(_params())) >= 256
+
+
+def test_python_layer_rejects_cpu_tensors():
+    import torch
+    import simplical_attn_b200 as sab
+    x = torch.zeros(1, 8, 1, 16)
+    with pytest.raises(RuntimeError):
+        sab.two_simplicial_attention(x, x, x, x, x, 4, 4)
+    m = sab.TwoSimplicialAttention(16, 4, 4)
+    assert len(m.state_dict()) == 0 and abs(m.scale - 0.25) < 1e-12
