@@ -1,0 +1,344 @@
+#!/usr/bin/env python3
+"""Benchmark of the 2-simplicial attention hot path (forward + backward) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload: the batch x head-parallel point the headline metric is quoted on -- B=16, H=Hkv=16,
+N=8192, D=128, w1=512, w2=32, bf16, forward + backward; with N GPUs each rank takes B/N sequences
+(no data-path collective; strong scaling).  Inputs are seeded N(0,1) synthetic tensors.
+
+One step = one forward and one backward over the rank's batch.  `value` is whole-job TFLOP/s with
+inputs resident in HBM, counting 16*B*H*N*w1*w2*D FLOPs per step (2 contractions forward, 6
+backward, 2*B*H*N*w1*w2*D each).  `e2e` is the same metric through the public call with pinned host
+buffers: host->device copies of the six inputs and device->host copies of O and the five
+gradients inside the timed region.  `roofline` describes the dominant kernel; `cpu_baseline`
+times the C loop oracle on the host cores on a bounded sample of the same workload.
+
+`--impl reference` times the reference's algorithm on the host cores (the C restatement of its
+loop; the reference itself is a Python triple loop that does not reach these sizes).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOAD = dict(B=16, H=16, Hkv=16, N=8192, D=128, w1=512, w2=32)
+FALLBACK_PEAKS = dict(bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, hbm_gbs=6650.0)
+
+
+def flops_unit(B, H, N, D, w1, w2):
+    return 2.0 * B * H * N * w1 * w2 * D
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [x for x in sm if x > 0.5 * max(sm)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_inputs(Bl, cfg, device, seed):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    shape_q = (Bl, cfg["N"], cfg["H"], cfg["D"])
+    shape_kv = (Bl, cfg["N"], cfg["Hkv"], cfg["D"])
+    host = [torch.randn(shape_q, generator=g).to(torch.bfloat16)]
+    host += [torch.randn(shape_kv, generator=g).to(torch.bfloat16) for _ in range(4)]
+    g1 = torch.Generator(device="cpu").manual_seed(seed + 1)
+    host.append(torch.randn(shape_q, generator=g1).to(torch.bfloat16))
+    host = [t.pin_memory() for t in host]
+    return host
+
+
+def cpu_oracle_rate(cfg, target_s=12.0, threads=None):
+    """TFLOP/s (same FLOP convention) of the C loop oracle on a bounded sample: one (batch, head)
+    slice of R query rows with full windows (halo rows in front), forward + backward."""
+    from oracle import c_oracle, simplicial_oracle as so
+    D, w1, w2 = cfg["D"], cfg["w1"], cfg["w2"]
+    scale = 1.0 / math.sqrt(D)
+    cores = c_oracle.num_threads()
+
+    def run(R):
+        q, k1, k2, v1, v2, do = so.make_inputs(1, R, 1, 1, D, seed=5, seed_do=6, halo1=w1 - 1, halo2=w2 - 1)
+        t0 = time.perf_counter()
+        c_oracle.forward(q, k1, k2, v1, v2, w1, w2, scale)
+        c_oracle.backward(q, k1, k2, v1, v2, do, w1, w2, scale)
+        return time.perf_counter() - t0
+
+    r0 = 32 * cores
+    t_probe = run(r0)
+    R = int(max(r0, min(64 * r0, r0 * target_s / max(t_probe, 1e-3))))
+    R = (R // (32 * cores)) * 32 * cores
+    t = run(R)
+    fl = 8.0 * flops_unit(1, 1, R, D, w1, w2)
+    return fl / t / 1e12, cores, R, t
+
+
+def run_reference_arm(args, cfg):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    per_step = []
+    rows = 0
+    cores = 0
+    for it in range(args.warmup + args.steps):
+        rate, cores, rows, t = cpu_oracle_rate(cfg, target_s=4.0)
+        if it >= args.warmup:
+            per_step.append((rate, t))
+    value = statistics.mean(r for r, _ in per_step)
+    ms = statistics.mean(t for _, t in per_step) * 1e3
+    sample = f"forward+backward of {rows} query rows of one (batch, head), full windows, per step"
+    line = {
+        "impl": "reference", "metric": "fwd+bwd TFLOP/s (N=8192,D=128,w1=512,w2=32)", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_name(cfg), **cfg, "parallelism": "host cores"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_name(cfg):
+    return (f"batch x head-parallel fwd+bwd B{cfg['B']} H{cfg['H']} Hkv{cfg['Hkv']} N{cfg['N']} D{cfg['D']} "
+            f"w1={cfg['w1']} w2={cfg['w2']}")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=None, help="override the global batch (profiling on a small case)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    cfg = dict(WORKLOAD)
+    if args.batch is not None:
+        cfg["B"] = args.batch
+    if args.impl == "reference":
+        run_reference_arm(args, cfg)
+        return
+
+    import simplical_attn_b200 as sab
+    from simplical_attn_b200 import _abi
+    import ctypes
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    if cfg["B"] % world != 0:
+        raise SystemExit(f"global batch {cfg['B']} is not divisible by {world} ranks")
+    Bl = cfg["B"] // world
+    D, w1, w2 = cfg["D"], cfg["w1"], cfg["w2"]
+    scale = 1.0 / math.sqrt(D)
+    _abi.load()
+
+    host = make_inputs(Bl, cfg, device, seed=100 * rank)
+    dev = [t.to(device, non_blocking=True) for t in host]
+    torch.cuda.synchronize()
+    q, k1, k2, v1, v2, do = dev
+
+    def step_resident():
+        o, lse = sab.two_simplicial_attn_fwd_kernel(q, k1, k2, v1, v2, w1, w2, scale)
+        grads = sab.two_simplicial_attn_bwd(q, k1, k2, v1, v2, o, lse, do, w1, w2, scale)
+        return o, grads
+
+    host_out = [torch.empty_like(h) for h in (host[0], host[0], host[1], host[2], host[3], host[4])]
+
+    def step_e2e():
+        d = [t.to(device, non_blocking=True) for t in host]
+        dq_in = d[0].requires_grad_(True)
+        kv = [t.requires_grad_(True) for t in d[1:5]]
+        o = sab.two_simplicial_attention(dq_in, *kv, w1, w2, scale)
+        o.backward(d[5])
+        outs = [o.detach(), dq_in.grad] + [t.grad for t in kv]
+        for dst, src in zip(host_out, outs):
+            dst.copy_(src, non_blocking=True)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        barrier()
+        ms = ev0.elapsed_time(ev1)
+        if dist is not None:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    # per-kernel timing for the roofline (CUDA events on the launching stream, after warm-up)
+    def time_phase(fn, reps):
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(reps):
+            fn()
+        ev1.record()
+        torch.cuda.synchronize()
+        return ev0.elapsed_time(ev1) / reps
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    lib = _abi.load()
+    for _ in range(args.warmup):
+        step_resident()
+    n0 = lib.sa_kernel_launches()
+    ms_step = timed(step_resident, args.steps, 0)
+    launches = int(lib.sa_kernel_launches() - n0)
+    clocks = sampler.stop() if sampler else None
+
+    o, lse = sab.two_simplicial_attn_fwd_kernel(q, k1, k2, v1, v2, w1, w2, scale)
+    ms_fwd = time_phase(lambda: sab.two_simplicial_attn_fwd_kernel(q, k1, k2, v1, v2, w1, w2, scale), max(2, args.steps))
+    ms_bwd = time_phase(lambda: sab.two_simplicial_attn_bwd(q, k1, k2, v1, v2, o, lse, do, w1, w2, scale),
+                        max(2, args.steps))
+    del o, lse
+
+    ms_e2e = None
+    if not args.no_e2e:
+        ms_e2e = timed(step_e2e, max(1, min(args.steps, 3)), 1)
+
+    unit_total = flops_unit(cfg["B"], cfg["H"], cfg["N"], D, w1, w2)
+    unit_rank = unit_total / world
+    value = 8.0 * unit_total / (ms_step * 1e-3) / 1e12
+
+    if rank == 0:
+        peaks, peak_kind = load_peaks()
+        peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+        p = _abi.Params()
+        p.B, p.N, p.H, p.Hkv, p.D, p.w1, p.w2 = Bl, cfg["N"], cfg["H"], cfg["Hkv"], D, w1, w2
+        p.dtype, p.algo, p.scale = _abi.SA_BF16, _abi.SA_ALGO_AUTO, scale
+        for nm, t in zip(("q", "k1", "k2", "v1", "v2", "o", "d_o", "dq", "dk1", "dk2", "dv1", "dv2"),
+                         (q, k1, k2, v1, v2, q, do, q, k1, k2, v1, v2)):
+            setattr(p, nm, _abi.Strides(t.stride(0), t.stride(1), t.stride(2)))
+        algo = _abi.load().sa_resolve_algo(ctypes.byref(p))
+        family = {1: "general (CUDA cores)", 2: "tcgen05"}.get(algo, str(algo))
+        # dominant phase: whichever of forward (2 units) / backward (6 units) takes longer
+        if ms_bwd >= ms_fwd:
+            dom, dom_ms, dom_fl = "backward", ms_bwd, 6.0 * unit_rank
+        else:
+            dom, dom_ms, dom_fl = "forward", ms_fwd, 2.0 * unit_rank
+        achieved = dom_fl / (dom_ms * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": f"{dom} ({family})", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "peak_source": f"{peak_kind} bf16 sustained", "traffic": None,
+                "frac_of_nominal_2250": achieved / 2250.0,
+                "forward": {"ms": ms_fwd, "tflops": 2.0 * unit_rank / (ms_fwd * 1e-3) / 1e12},
+                "backward": {"ms": ms_bwd, "tflops": 6.0 * unit_rank / (ms_bwd * 1e-3) / 1e12}}
+        line = {
+            "metric": "fwd+bwd TFLOP/s (N=8192,D=128,w1=512,w2=32)", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": workload_name(cfg), **cfg, "parallelism": f"batch split over {world} GPU(s)",
+                       "l2": "inputs (6 x %.0f MB per rank) exceed the 126 MB L2" % (q.numel() * 2 / 1e6),
+                       "kernels": family},
+            "frac_of_peak": {"measured_sustained": value / world / peak, "nominal_2250": value / world / 2250.0},
+            "clocks": clocks, "gpu_launches": launches, "roofline": roof,
+        }
+        if ms_e2e is not None:
+            h2d = sum(t.numel() * t.element_size() for t in host)
+            d2h = sum(t.numel() * t.element_size() for t in host_out)
+            line["e2e"] = {"value": 8.0 * unit_total / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        if world == 1 and not args.no_cpu_baseline:
+            rate, cores, rows, t = cpu_oracle_rate(cfg)
+            line["cpu_baseline"] = {"value": rate, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                                    "sample": f"C loop oracle, forward+backward of {rows} query rows of one "
+                                              f"(batch, head) with full windows, {t:.1f} s"}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

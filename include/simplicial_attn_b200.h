@@ -65,7 +65,8 @@ typedef struct {
  * TwoSimplicialAttentionFunction.forward (simplicial/triton_impl.py:19-58; kernel
  * simplicial/kernels.py:11-171).  Writes O (dtype) and LSE (fp32, natural log; the reference's
  * `M`, simplicial/kernels.py:164-167).  `workspace` must hold sa_forward_workspace_size() bytes,
- * 256-byte aligned. */
+ * 256-byte aligned; its first 256 bytes hold the device status word and must be zero before the
+ * first call that uses the buffer (the library never clears them except in sa_read_status). */
 int sa_forward(const sa_params* p, const void* q, const void* k1, const void* k2, const void* v1,
                const void* v2, void* o, float* lse, void* workspace, size_t workspace_bytes, void* stream);
 
@@ -92,6 +93,10 @@ int sa_read_status(void* workspace, void* stream);
 /* Which kernel family AUTO resolves to for `p` (SA_ALGO_GENERAL or SA_ALGO_TCGEN05), or a negative
  * sa_status if `p` is invalid. */
 int sa_resolve_algo(const sa_params* p);
+
+/* Number of kernels this library has launched in this process so far (all devices, all streams).
+ * No counterpart in the reference. */
+uint64_t sa_kernel_launches(void);
 
 const char* sa_strerror(int status);
 int sa_version(void);

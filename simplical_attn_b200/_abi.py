@@ -16,7 +16,7 @@ SA_BF16, SA_F16, SA_F32 = 0, 1, 2
 SA_ALGO_AUTO, SA_ALGO_GENERAL, SA_ALGO_TCGEN05 = 0, 1, 2
 
 EXPORTS = ("sa_forward", "sa_backward", "sa_forward_workspace_size", "sa_backward_workspace_size", "sa_read_status",
-           "sa_resolve_algo", "sa_strerror", "sa_version")
+           "sa_resolve_algo", "sa_strerror", "sa_version", "sa_kernel_launches")
 
 
 class Strides(ctypes.Structure):
@@ -68,6 +68,7 @@ def load():
     lib.sa_strerror.argtypes = [ctypes.c_int]
     lib.sa_strerror.restype = ctypes.c_char_p
     lib.sa_version.restype = ctypes.c_int
+    lib.sa_kernel_launches.restype = ctypes.c_uint64
     _lib = lib
     return lib
 

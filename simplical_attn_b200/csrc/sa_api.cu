@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "sa_common.cuh"
@@ -16,6 +17,8 @@ namespace {
 using sa::KParams;
 
 constexpr size_t kStatusBytes = 256;
+
+std::atomic<uint64_t> g_launches{0};      // kernels launched by this library in this process
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 bool stride_ok8(const sa_strides& s) { return s.b % 8 == 0 && s.n % 8 == 0 && s.h % 8 == 0; }
@@ -155,6 +158,7 @@ int launch_fwd_tc(const sa_params* p, const KParams& k, const void* q, const voi
                                                                       (__nv_bfloat16*)o, lse);
     }
     (void)p;
+    g_launches += 1;
     return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
 }
 
@@ -170,6 +174,8 @@ int resolve(const sa_params* p, bool backward) {
 extern "C" {
 
 int sa_version(void) { return 100; }
+
+uint64_t sa_kernel_launches(void) { return g_launches.load(); }
 
 const char* sa_strerror(int status) {
     switch (status) {
@@ -231,6 +237,7 @@ int sa_forward(const sa_params* p, const void* q, const void* k1, const void* k2
     }
     if (algo == SA_ALGO_TCGEN05) return launch_fwd_tc(p, k, q, k1, k2, v1, v2, o, lse, workspace, st);
     const cudaError_t e = sa::general::launch_fwd(p->dtype, k, q, k1, k2, v1, v2, o, lse, st);
+    g_launches += 1;
     (void)elem_size;
     return e == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
 }
@@ -255,13 +262,16 @@ int sa_backward(const sa_params* p, const void* q, const void* k1, const void* k
         algo = SA_ALGO_GENERAL;
     }
     if (algo == SA_ALGO_TCGEN05) {
+        int nlaunch = 0;
         const int rc = sa::tc::launch_bwd(k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2,
                                           static_cast<uint8_t*>(workspace) + kStatusBytes,
-                                          reinterpret_cast<sa::DeviceStatus*>(workspace), st);
+                                          reinterpret_cast<sa::DeviceStatus*>(workspace), st, &nlaunch);
+        g_launches += nlaunch;
         if (rc != -1) return rc;      // -1: the tensor-core backward declines this problem
         if (p->algo == SA_ALGO_TCGEN05) return SA_ERR_UNSUPPORTED;
     }
     const cudaError_t e = sa::general::launch_bwd(p->dtype, k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2, st);
+    g_launches += (dq ? 1 : 0) + ((dk1 || dv1) ? 1 : 0) + ((dk2 || dv2) ? 1 : 0);
     return e == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
 }
 
