@@ -262,10 +262,12 @@ int sa_backward(const sa_params* p, const void* q, const void* k1, const void* k
         algo = SA_ALGO_GENERAL;
     }
     if (algo == SA_ALGO_TCGEN05) {
+        if (device_info().cc_major != 10) return SA_ERR_NOT_SM100;
         int nlaunch = 0;
         const int rc = sa::tc::launch_bwd(k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2,
                                           static_cast<uint8_t*>(workspace) + kStatusBytes,
-                                          reinterpret_cast<sa::DeviceStatus*>(workspace), st, &nlaunch);
+                                          reinterpret_cast<sa::DeviceStatus*>(workspace), st, &nlaunch, &make_map,
+                                          device_info().sm_count);
         g_launches += nlaunch;
         if (rc != -1) return rc;      // -1: the tensor-core backward declines this problem
         if (p->algo == SA_ALGO_TCGEN05) return SA_ERR_UNSUPPORTED;

@@ -1,4 +1,34 @@
-// Backward 2-simplicial attention on the sm_100a tensor cores.
+// Backward 2-simplicial attention on the sm_100a tensor cores.  Replaces the reference's
+// compute_D_kernel, two_simplicial_attn_bwd_kv1_kernel and two_simplicial_attn_bwd_kv2_kernel
+// (simplicial/kernels.py:569-571, :175-382, :386-566) without atomics.
+//
+// Virtual rows as in the forward: rho = i * DW + delta (DW = w2 rounded up to a power of two),
+// k = i - delta,  A[rho,:] = Q_i * (K2_k + k2_bias),  C[rho,:] = dO_i * (V2_k + v2_bias).  With
+//   S = A K1^T,  P = exp2(S*scale*log2e - LSE2_i),  dP = C V1^T,  dS = P * (dP - Delta_i)
+// the gradients are
+//   dV1 = P^T C          dK1 = scale * dS^T A                              ("column" kernel)
+//   G = dS K1,  U = P V1                                                   ("row" kernel)
+//   dQ_i = scale * sum_delta G[rho] * (K2_k + bias)
+//   dK2_k = scale * sum_i G[(i, i-k)] * Q_i        dV2_k = sum_i U[(i, i-k)] * dO_i
+//
+// Three launches plus a tiny one:
+//   1. prep_kernel      Delta_i = dO_i . O_i and LSE2_i = LSE_i * log2e                (fp32)
+//   2. bwd_col_kernel   a block owns 128 K1/V1 rows of one KV head, streams 64-row tiles of A and C
+//                       (formed on chip) for every query head of the group, accumulates dV1 and
+//                       dK1 in tensor memory and writes them once.
+//   3. bwd_row_kernel   a block owns a run of consecutive queries of one query head; per 128-row
+//                       tile it streams 64-row K1/V1 tiles by TMA, accumulates U and G in tensor
+//                       memory, merges G over delta into dQ and adds the per-K2-row sums of G*Q and
+//                       U*dO into fp32 partial buffers in the workspace (plain read-modify-write:
+//                       a row is only ever touched by one block, in program order).
+//   4. kv2_reduce_kernel sums those partials over the query heads of a group and over run
+//                       boundaries and writes dK2, dV2.
+//
+// Both big kernels share one pipeline: S and dP tiles (128 lanes x 64 columns) are double buffered
+// in tensor memory; softmax group b (4 warps) turns buffer b into P and dS (bf16, in place) while the
+// tensor cores work on the other buffer; P and dS then feed the two accumulating MMAs from tensor
+// memory.  Warps 0-3 / 4-7: softmax groups, 8-11: tile producer (column kernel only), 12: MMA
+// issuer, 13: TMA issuer.
 #pragma once
 
 #include "sa_ptx.cuh"
@@ -6,16 +36,933 @@
 namespace sa {
 namespace tc {
 
-inline size_t bwd_workspace_bytes(const KParams& k) {
-    (void)k;
-    return 0;
+constexpr int kBwdThreads = 512;
+constexpr int kStreamRows = 64;        // rows of a streamed tile = columns of an S / dP tile
+constexpr int kBwdStages = 3;          // streamed-tile ring depth
+
+struct BwdTcParams {
+    KParams k;
+    int dw_log2;
+    // column kernel
+    int num_jtiles;          // ceil(n1 / 128)
+    long num_col_items;      // B * Hkv * num_jtiles
+    // row kernel
+    int units_per_run;       // 128-row tiles per run
+    int num_runs;            // runs per (b, h)
+    long num_row_items;      // B * H * num_runs
+    const float* lse2;       // [B,H,N]
+    const float* delta;      // [B,H,N]
+    float* ws_full_k2;       // [B,H,N,D]   fp32 partial dK2 of rows k = i + halo2
+    float* ws_full_v2;
+    float* ws_head_k2;       // [B,H,num_runs,w2-1,D]  partials for the rows just before a run
+    float* ws_head_v2;
+    DeviceStatus* status;
+};
+
+template <int HD>
+struct BwdSmem {
+    static constexpr int kSlabs = HD / 64;
+    static constexpr int kBigTile = 128 * HD * 2;            // stationary tile  [128 x HD]
+    static constexpr int kBigSlab = 128 * 128;
+    static constexpr int kSmallTile = kStreamRows * HD * 2;  // streamed tile    [64 x HD]
+    static constexpr int kSmallSlab = kStreamRows * 128;
+    static constexpr int kStat0 = 0;                         // K1 (column kernel) / A (row kernel)
+    static constexpr int kStat1 = kBigTile;                  // V1 / C
+    static constexpr int kStream = 2 * kBigTile;             // kBwdStages x (tile0 | tile1)
+    static constexpr int kMeta = kStream + kBwdStages * 2 * kSmallTile;   // per stage: 64 lse2 + 64 delta
+    static constexpr int kBars = kMeta + kBwdStages * 128 * 4;
+    static constexpr int kNumBars = 2 * kBwdStages + 10;
+    static constexpr int kMisc = kBars + kNumBars * 8;
+    static constexpr int kTotal = kMisc + 16;
+    static constexpr int kAlloc = (kTotal + 1024 > 120 * 1024) ? kTotal + 1024 : 120 * 1024;
+};
+
+// ------------------------------------------------------------------------------------------------
+// 1. Delta and LSE2
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+prep_kernel(KParams p, const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+            const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ delta) {
+    const long row = (long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= (long)p.B * p.H * p.N) return;
+    const int i = (int)(row % p.N);
+    const int h = (int)((row / p.N) % p.H);
+    const int b = (int)(row / p.N / p.H);
+    const __nv_bfloat16* orow = o + b * p.o.b + (long)i * p.o.n + h * p.o.h;
+    const __nv_bfloat16* drow = d_o + b * p.d_o.b + (long)i * p.d_o.n + h * p.d_o.h;
+    float s = 0.f;
+    for (int d = lane * 2; d < p.D; d += 64) {
+        const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)(orow + d));
+        const float2 c = __bfloat1622float2(*(const __nv_bfloat162*)(drow + d));
+        s = fmaf(a.x, c.x, s);
+        s = fmaf(a.y, c.y, s);
+    }
+    s = warp_sum(s);
+    if (lane == 0) {
+        delta[row] = s;
+        lse2[row] = lse[row] * kLog2e;
+    }
 }
+
+// Product of two bf16 rows (x * (y + bias)), 8 elements per 16-byte chunk, rounded once to bf16.
+__device__ __forceinline__ uint4 mul_chunk(const uint4& xa, const uint4& ya, float bias) {
+    const __nv_bfloat162* xh = (const __nv_bfloat162*)&xa;
+    const __nv_bfloat162* yh = (const __nv_bfloat162*)&ya;
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 xf = __bfloat1622float2(xh[e]);
+        const float2 yf = __bfloat1622float2(yh[e]);
+        w[e] = ptx::pack_bf16(xf.x * (yf.x + bias), xf.y * (yf.y + bias));
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Writes row `row` of a 128-byte-swizzled tile made of [rows x 64] slabs `slab_bytes` apart:
+// out = x * (y + bias) over HD elements, or zeros.
+template <int HD>
+__device__ __forceinline__ void form_row(uint8_t* tile, int slab_bytes, int row, bool valid, const __nv_bfloat16* x,
+                                         const __nv_bfloat16* y, float bias) {
+#pragma unroll
+    for (int c = 0; c < HD / 8; ++c) {
+        uint4 out = make_uint4(0, 0, 0, 0);
+        if (valid) out = mul_chunk(((const uint4*)x)[c], ((const uint4*)y)[c], bias);
+        *(uint4*)(tile + (c >> 3) * slab_bytes + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = out;
+    }
+}
+
+// P = mask ? exp2(s*c2 - lse2) : 0 and dS = P * (dp - delta) for 32 columns, packed to bf16.
+// MASKED selects per-column validity through lo/hi (tile-relative valid column range).
+template <bool MASKED>
+__device__ __forceinline__ void softmax_bwd_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], int c0, int lo, int hi,
+                                                  float c2, float lse2, float delta, uint32_t (&pp)[16], uint32_t (&ds)[16]) {
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+        float p0 = ptx::ex2(fmaf(__uint_as_float(s[e]), c2, -lse2));
+        float p1 = ptx::ex2(fmaf(__uint_as_float(s[e + 1]), c2, -lse2));
+        if (MASKED) {
+            const int c = c0 + e;
+            p0 = (c >= lo && c <= hi) ? p0 : 0.f;
+            p1 = (c + 1 >= lo && c + 1 <= hi) ? p1 : 0.f;
+        }
+        float d0 = p0 * (__uint_as_float(dp[e]) - delta);
+        float d1 = p1 * (__uint_as_float(dp[e + 1]) - delta);
+        if (MASKED) {      // a masked column may hold stale tensor-memory contents (NaN): select, never multiply
+            const int c = c0 + e;
+            d0 = (c >= lo && c <= hi) ? d0 : 0.f;
+            d1 = (c + 1 >= lo && c + 1 <= hi) ? d1 : 0.f;
+        }
+        pp[e >> 1] = ptx::pack_bf16(p0, p1);
+        ds[e >> 1] = ptx::pack_bf16(d0, d1);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// 2. Column kernel: dK1, dV1
+// ------------------------------------------------------------------------------------------------
+struct ColItem {
+    int b, hk, j0;        // first K1/V1 buffer row of the block's 128-row tile
+    int tt_lo, ntq;       // first streamed tile (64 virtual rows each) and tiles per query head
+};
+
+__device__ __forceinline__ ColItem col_item(const BwdTcParams& P, long it) {
+    const KParams& p = P.k;
+    ColItem c;
+    const int jt = (int)(it % P.num_jtiles);
+    const long bh = it / P.num_jtiles;
+    c.hk = (int)(bh % p.Hkv);
+    c.b = (int)(bh / p.Hkv);
+    c.j0 = jt * 128;
+    // queries whose K1 window meets rows [j0, j0+128)
+    const int i_lo = max(0, c.j0 - p.halo1);
+    const int i_hi = min(p.N - 1, c.j0 + 127 - p.halo1 + p.w1 - 1);
+    if (i_hi < i_lo) {
+        c.tt_lo = 0;
+        c.ntq = 0;
+    } else {
+        const long r_lo = (long)i_lo << P.dw_log2, r_hi = ((long)(i_hi + 1) << P.dw_log2);   // [r_lo, r_hi)
+        c.tt_lo = (int)(r_lo / kStreamRows);
+        c.ntq = (int)((r_hi + kStreamRows - 1) / kStreamRows) - c.tt_lo;
+    }
+    return c;
+}
+
+
+// Barrier block shared by the two big kernels.
+struct BwdBars {
+    uint64_t* st_full;     // [kBwdStages] streamed tile ready
+    uint64_t* st_empty;    // [kBwdStages] streamed tile consumed (tcgen05.commit)
+    uint64_t* sdp_ready;   // [2] S and dP of buffer b computed (commit)
+    uint64_t* pds_ready;   // [2] P and dS of buffer b stored (128 arrivals)
+    uint64_t* stat_full;   // stationary tiles ready
+    uint64_t* stat_empty;  // stationary tiles no longer read (commit)
+    uint64_t* acc_ready;   // accumulators final (commit)
+    uint64_t* acc_free;    // accumulators read out (256 arrivals)
+};
+
+__device__ __forceinline__ BwdBars bwd_bars(uint64_t* b) {
+    return BwdBars{b, b + kBwdStages, b + 2 * kBwdStages, b + 2 * kBwdStages + 2, b + 2 * kBwdStages + 4,
+                   b + 2 * kBwdStages + 5, b + 2 * kBwdStages + 6, b + 2 * kBwdStages + 7};
+}
+
+// The MMAs of one streamed tile.  `X`, `Y`: stationary tiles [128 x HD]; `W`, `Z`: streamed tiles
+// [64 x HD] of which the first `width` rows count.
+//   S_b  = X W^T,   dP_b = Y Z^T              (issue_sdp)
+//   acc1 += P_b Z,  acc2 += dS_b W            (issue_acc; P_b, dS_b read from tensor memory)
+template <int HD>
+__device__ __forceinline__ void issue_sdp(uint32_t tm_s, uint32_t tm_dp, uint32_t x, uint32_t y, uint32_t w, uint32_t z,
+                                          int width) {
+    using L = BwdSmem<HD>;
+    const uint32_t idesc = ptx::make_idesc(128, width, false, false);
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk)
+        ptx::mma_ss(tm_s, ptx::desc_kmajor(x + (kk >> 2) * L::kBigSlab, kk & 3),
+                    ptx::desc_kmajor(w + (kk >> 2) * L::kSmallSlab, kk & 3), idesc, kk > 0);
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk)
+        ptx::mma_ss(tm_dp, ptx::desc_kmajor(y + (kk >> 2) * L::kBigSlab, kk & 3),
+                    ptx::desc_kmajor(z + (kk >> 2) * L::kSmallSlab, kk & 3), idesc, kk > 0);
+}
+
+template <int HD>
+__device__ __forceinline__ void issue_acc(uint32_t tm_acc1, uint32_t tm_acc2, uint32_t tm_p, uint32_t tm_ds, uint32_t w,
+                                          uint32_t z, int width, bool accumulate) {
+    using L = BwdSmem<HD>;
+    const uint32_t idesc = ptx::make_idesc(128, HD, false, true);
+    const int ksteps = width / 16;
+    for (int kk = 0; kk < ksteps; ++kk)
+        ptx::mma_ts(tm_acc1, tm_p + kk * 8, ptx::desc_mnmajor(z + kk * 2048, L::kSmallSlab), idesc, accumulate || kk > 0);
+    for (int kk = 0; kk < ksteps; ++kk)
+        ptx::mma_ts(tm_acc2, tm_ds + kk * 8, ptx::desc_mnmajor(w + kk * 2048, L::kSmallSlab), idesc, accumulate || kk > 0);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
+               const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
+               const __nv_bfloat16* __restrict__ k2, const __nv_bfloat16* __restrict__ v2,
+               const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dk1, __nv_bfloat16* __restrict__ dv1) {
+    using L = BwdSmem<HD>;
+    using namespace ptx;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    const KParams& p = P.k;
+    const BwdBars B = bwd_bars((uint64_t*)(smem + L::kBars));
+    uint32_t* tmem_slot = (uint32_t*)(smem + L::kMisc);
+    volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
+    const WaitCtx wctx{abort_flag, P.status};
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kBwdStages; ++s) {
+            mbar_init(&B.st_full[s], 128);
+            mbar_init(&B.st_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&B.sdp_ready[b], 1);
+            mbar_init(&B.pds_ready[b], 128);
+        }
+        mbar_init(B.stat_full, 1);
+        mbar_init(B.stat_empty, 1);
+        mbar_init(B.acc_ready, 1);
+        mbar_init(B.acc_free, 256);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 12) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tm_s[2] = {tmem_base, tmem_base + 64};
+    const uint32_t tm_dp[2] = {tmem_base + 128, tmem_base + 192};
+    const uint32_t tm_dv1 = tmem_base + 256, tm_dk1 = tmem_base + 384;
+    const int DW = 1 << P.dw_log2;
+
+    if (warp < 8) {
+        // ---------------------------------------------------------------- softmax groups + epilogue
+        const int grp = warp >> 2;
+        const int row = tid & 127;                       // tensor-memory lane = K1/V1 row of the tile
+        const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
+        const float c2 = p.scale * kLog2e;
+        uint32_t n_mine = 0, n_items = 0, g_base = 0;
+        for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
+            const ColItem ci = col_item(P, it);
+            const int jb = ci.j0 + row;
+            const int nt = ci.ntq * p.G;
+            for (int t = grp; t < nt; t += 2, ++n_mine) {
+                const int stage = (int)((g_base + t) % kBwdStages);
+                const float* m_lse = (const float*)(smem + L::kMeta) + stage * 128;
+                const float* m_delta = m_lse + 64;
+                const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kStreamRows;
+                const int iq0 = (int)(rho0 >> P.dw_log2);
+                mbar_wait(&B.sdp_ready[grp], n_mine & 1, wctx, 20);
+                tc_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < kStreamRows; c0 += 32) {
+                    uint32_t s[32], dp[32], pp[16], ds[16];
+                    tmem_ld32(tm_s[grp] + lane_addr + c0, s);
+                    tmem_ld32(tm_dp[grp] + lane_addr + c0, dp);
+                    tmem_wait_ld();
+                    if (P.dw_log2 >= 5) {
+                        // the 32 columns belong to one query
+                        const int i = (int)((rho0 + c0) >> P.dw_log2);
+                        const bool valid = (jb <= i + p.halo1) && (jb >= i + p.halo1 - p.w1 + 1);
+                        softmax_bwd_chunk<true>(s, dp, 0, valid ? 0 : 1, valid ? 31 : 0, c2, m_lse[i - iq0], m_delta[i - iq0],
+                                                pp, ds);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 2) {
+                            float pv[2], dv[2];
+#pragma unroll
+                            for (int x = 0; x < 2; ++x) {
+                                const int i = (int)((rho0 + c0 + e + x) >> P.dw_log2);
+                                const bool valid = (jb <= i + p.halo1) && (jb >= i + p.halo1 - p.w1 + 1);
+                                const float pe = ex2(fmaf(__uint_as_float(s[e + x]), c2, -m_lse[i - iq0]));
+                                pv[x] = valid ? pe : 0.f;
+                                dv[x] = valid ? pe * (__uint_as_float(dp[e + x]) - m_delta[i - iq0]) : 0.f;
+                            }
+                            pp[e >> 1] = pack_bf16(pv[0], pv[1]);
+                            ds[e >> 1] = pack_bf16(dv[0], dv[1]);
+                        }
+                    }
+                    tmem_st16(tm_s[grp] + lane_addr + (c0 >> 1), pp);
+                    tmem_st16(tm_dp[grp] + lane_addr + (c0 >> 1), ds);
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&B.pds_ready[grp]);
+            }
+            g_base += nt;
+            // epilogue: group 0 writes dV1, group 1 writes dK1 (times scale)
+            __nv_bfloat16* out = grp == 0 ? dv1 : dk1;
+            const sa_strides st = grp == 0 ? p.dv1 : p.dk1;
+            const float mult = grp == 0 ? 1.f : p.scale;
+            if (nt > 0) {
+                mbar_wait(B.acc_ready, n_items & 1, wctx, 21);
+                ++n_items;
+                tc_fence_after();
+            }
+            const uint32_t acc = (grp == 0 ? tm_dv1 : tm_dk1) + lane_addr;
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t v[32];
+                if (nt > 0) {
+                    tmem_ld32(acc + c0, v);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) v[e] = 0u;
+                }
+                if (out != nullptr && jb < p.n1) {
+                    uint4* dst = (uint4*)(out + ci.b * st.b + (long)jb * st.n + ci.hk * st.h + c0);
+#pragma unroll
+                    for (int x = 0; x < 4; ++x)
+                        dst[x] = make_uint4(pack_bf16(__uint_as_float(v[8 * x]) * mult, __uint_as_float(v[8 * x + 1]) * mult),
+                                            pack_bf16(__uint_as_float(v[8 * x + 2]) * mult, __uint_as_float(v[8 * x + 3]) * mult),
+                                            pack_bf16(__uint_as_float(v[8 * x + 4]) * mult, __uint_as_float(v[8 * x + 5]) * mult),
+                                            pack_bf16(__uint_as_float(v[8 * x + 6]) * mult, __uint_as_float(v[8 * x + 7]) * mult));
+                }
+            }
+            if (nt > 0) {
+                tc_fence_before();
+                mbar_arrive(B.acc_free);
+            }
+        }
+    } else if (warp < 12) {
+        // ---------------------------------------------------------------- producer of the A / C tiles
+        const int ptid = tid - 256;
+        const int prow = ptid & 63;
+        const int which = ptid >> 6;                      // 0: A = Q * K2, 1: C = dO * V2
+        uint32_t g_base = 0;
+        for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
+            const ColItem ci = col_item(P, it);
+            const int nt = ci.ntq * p.G;
+            for (int t = 0; t < nt; ++t) {
+                const uint32_t g = g_base + t;
+                const int stage = (int)(g % kBwdStages);
+                const int h = ci.hk * p.G + t / ci.ntq;
+                const int tt = ci.tt_lo + (t % ci.ntq);
+                const long rho = (long)tt * kStreamRows + prow;
+                const int i = (int)(rho >> P.dw_log2);
+                const int dlt = (int)(rho & (DW - 1));
+                const int kb = i + p.halo2 - dlt;
+                const bool valid = (i < p.N) && (dlt < p.w2) && (kb >= 0);
+                const int ic = min(i, p.N - 1), kc = max(kb, 0);
+                mbar_wait(&B.st_empty[stage], ((g / kBwdStages) & 1) ^ 1, wctx, 22);
+                uint8_t* tile = smem + L::kStream + stage * 2 * L::kSmallTile + which * L::kSmallTile;
+                if (which == 0) {
+                    form_row<HD>(tile, L::kSmallSlab, prow, valid, q + ci.b * p.q.b + (long)ic * p.q.n + h * p.q.h,
+                                 k2 + ci.b * p.k2.b + (long)kc * p.k2.n + ci.hk * p.k2.h, p.k2_bias);
+                    if (prow == 0 || dlt == 0) {
+                        const int qidx = i - (int)(((long)tt * kStreamRows) >> P.dw_log2);
+                        float* m_lse = (float*)(smem + L::kMeta) + stage * 128;
+                        const long li = ((long)ci.b * p.H + h) * p.N + ic;
+                        m_lse[qidx] = (i < p.N) ? P.lse2[li] : INFINITY;
+                        m_lse[64 + qidx] = (i < p.N) ? P.delta[li] : 0.f;
+                    }
+                } else {
+                    form_row<HD>(tile, L::kSmallSlab, prow, valid, d_o + ci.b * p.d_o.b + (long)ic * p.d_o.n + h * p.d_o.h,
+                                 v2 + ci.b * p.v2.b + (long)kc * p.v2.n + ci.hk * p.v2.h, p.v2_bias);
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(&B.st_full[stage]);
+            }
+            g_base += nt;
+        }
+    } else if (warp == 12) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            uint32_t nb[2] = {0, 0}, g_base = 0, n_items = 0;
+            const uint32_t k1s = smem_base + L::kStat0, v1s = smem_base + L::kStat1;
+            for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
+                const ColItem ci = col_item(P, it);
+                const int nt = ci.ntq * p.G;
+                if (nt == 0) continue;
+                mbar_wait(B.stat_full, n_items & 1, wctx, 23);
+                if (n_items > 0) mbar_wait(B.acc_free, (n_items - 1) & 1, wctx, 24);
+                tc_fence_after();
+                for (int t = 0; t <= nt; ++t) {
+                    if (t < nt) {
+                        const uint32_t g = g_base + t;
+                        const int stage = (int)(g % kBwdStages), b = t & 1;
+                        const uint32_t a_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, c_t = a_t + L::kSmallTile;
+                        mbar_wait(&B.st_full[stage], (g / kBwdStages) & 1, wctx, 25);
+                        tc_fence_after();
+                        issue_sdp<HD>(tm_s[b], tm_dp[b], k1s, v1s, a_t, c_t, kStreamRows);
+                        tc_commit(&B.sdp_ready[b]);
+                    }
+                    if (t >= 1) {
+                        const int tp = t - 1;
+                        const uint32_t g = g_base + tp;
+                        const int stage = (int)(g % kBwdStages), b = tp & 1;
+                        const uint32_t a_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, c_t = a_t + L::kSmallTile;
+                        mbar_wait(&B.pds_ready[b], nb[b] & 1, wctx, 26);
+                        ++nb[b];
+                        tc_fence_after();
+                        // dV1 += P^T-tile * C-tile ; dK1 += dS^T-tile * A-tile
+                        issue_acc<HD>(tm_dv1, tm_dk1, tm_s[b], tm_dp[b], a_t, c_t, kStreamRows, tp > 0);
+                        tc_commit(&B.st_empty[stage]);
+                    }
+                }
+                tc_commit(B.acc_ready);
+                tc_commit(B.stat_empty);
+                g_base += nt;
+                ++n_items;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 13) {
+        // ---------------------------------------------------------------- TMA: the block's K1 / V1 rows
+        if (lane == 0) {
+            prefetch_tensormap(&map_k1);
+            prefetch_tensormap(&map_v1);
+            uint32_t n = 0;
+            for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
+                const ColItem ci = col_item(P, it);
+                if (ci.ntq == 0) continue;
+                mbar_wait(B.stat_empty, (n & 1) ^ 1, wctx, 27);
+                mbar_arrive_expect_tx(B.stat_full, 2 * L::kBigTile);
+#pragma unroll
+                for (int sl = 0; sl < L::kSlabs; ++sl) {
+                    tma_load_4d(smem + L::kStat0 + sl * L::kBigSlab, &map_k1, B.stat_full, sl * 64, ci.j0, ci.hk, ci.b);
+                    tma_load_4d(smem + L::kStat1 + sl * L::kBigSlab, &map_v1, B.stat_full, sl * 64, ci.j0, ci.hk, ci.b);
+                }
+                ++n;
+            }
+        }
+        __syncwarp();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 12) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// 3. Row kernel: dQ and the per-query-head partial sums of dK2, dV2
+// ------------------------------------------------------------------------------------------------
+struct RowUnit {
+    int i0;            // first query of the 128-row tile
+    int col_start;     // first K1/V1 buffer row needed
+    int nt;            // streamed 64-row tiles
+    int last_width;    // width of the last one (multiple of 16)
+};
+
+__device__ __forceinline__ RowUnit row_unit(const BwdTcParams& P, int i0) {
+    const KParams& p = P.k;
+    RowUnit u;
+    const int qpt = 128 >> P.dw_log2;
+    u.i0 = i0;
+    const int i_last = min(i0 + qpt, p.N) - 1;
+    u.col_start = max(0, i0 + p.halo1 - p.w1 + 1);
+    const int ncols = i_last + p.halo1 - u.col_start + 1;
+    u.nt = (ncols + kStreamRows - 1) / kStreamRows;
+    u.last_width = ((ncols - (u.nt - 1) * kStreamRows) + 15) & ~15;
+    return u;
+}
+
+struct RowItem {
+    int b, h, hk, run, i_run0, i_run1;     // queries [i_run0, i_run1)
+};
+
+__device__ __forceinline__ RowItem row_item(const BwdTcParams& P, long it) {
+    const KParams& p = P.k;
+    RowItem r;
+    r.run = (int)(it % P.num_runs);
+    const long bh = it / P.num_runs;
+    r.h = (int)(bh % p.H);
+    r.b = (int)(bh / p.H);
+    r.hk = r.h / p.G;
+    const int runq = P.units_per_run * (128 >> P.dw_log2);
+    r.i_run0 = r.run * runq;
+    r.i_run1 = min(p.N, r.i_run0 + runq);
+    return r;
+}
+
+// Loads CW consecutive fp32 accumulator columns of this thread's tensor-memory lane.
+template <int CW>
+__device__ __forceinline__ void tmem_ld_cw(uint32_t addr, uint32_t (&v)[CW]) {
+    if constexpr (CW == 32) ptx::tmem_ld32(addr, v);
+    else ptx::tmem_ld16(addr, v);
+    ptx::tmem_wait_ld();
+}
+
+// CW bf16 values of a row starting at element `col`, plus `bias`, as floats.
+template <int CW>
+__device__ __forceinline__ void load_bf16_cw(const __nv_bfloat16* row, int col, float bias, float (&out)[CW]) {
+#pragma unroll
+    for (int x = 0; x < CW / 8; ++x) {
+        const uint4 raw = ((const uint4*)(row + col))[x];
+        const __nv_bfloat162* h2 = (const __nv_bfloat162*)&raw;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h2[e]);
+            out[8 * x + 2 * e] = f.x + bias;
+            out[8 * x + 2 * e + 1] = f.y + bias;
+        }
+    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
+               const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
+               const __nv_bfloat16* __restrict__ k2, const __nv_bfloat16* __restrict__ v2,
+               const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dq, int need_kv2) {
+    using L = BwdSmem<HD>;
+    using namespace ptx;
+    constexpr int CW = HD / 4;                            // epilogue chunk width
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    const KParams& p = P.k;
+    const BwdBars B = bwd_bars((uint64_t*)(smem + L::kBars));
+    uint32_t* tmem_slot = (uint32_t*)(smem + L::kMisc);
+    volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
+    const WaitCtx wctx{abort_flag, P.status};
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < kBwdStages; ++s) {
+            mbar_init(&B.st_full[s], 1);
+            mbar_init(&B.st_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&B.sdp_ready[b], 1);
+            mbar_init(&B.pds_ready[b], 128);
+        }
+        mbar_init(B.stat_full, 256);       // A and C formed by the two softmax groups
+        mbar_init(B.stat_empty, 1);
+        mbar_init(B.acc_ready, 1);
+        mbar_init(B.acc_free, 256);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 12) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tm_s[2] = {tmem_base, tmem_base + 64};
+    const uint32_t tm_dp[2] = {tmem_base + 128, tmem_base + 192};
+    const uint32_t tm_u = tmem_base + 256, tm_g = tmem_base + 384;     // U = P V1, G = dS K1
+    const int DW = 1 << P.dw_log2;
+    const int qpt = 128 >> P.dw_log2;
+
+    if (warp < 8) {
+        // ---------------------------------------------------------------- softmax groups + epilogue
+        const int grp = warp >> 2;
+        const int row = tid & 127;
+        const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
+        const int qq = row >> P.dw_log2;
+        const int dlt = row & (DW - 1);
+        const float c2 = p.scale * kLog2e;
+        uint8_t* my_tile = smem + (grp == 0 ? L::kStat0 : L::kStat1);      // group 0 forms A, group 1 forms C
+        float* scr_a = (float*)my_tile;                   // [128][CW] fp32, column index XOR-swizzled by the row
+        float* scr_b = scr_a + 128 * CW;
+        uint32_t n_mine = 0, n_units = 0;
+        for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
+            const RowItem ri = row_item(P, it);
+            for (int i0 = ri.i_run0, uidx = 0; i0 < ri.i_run1; i0 += qpt, ++uidx, ++n_units) {
+                const RowUnit ru = row_unit(P, i0);
+                const int i = i0 + qq;
+                const int kb = i + p.halo2 - dlt;
+                const bool row_valid = (i < p.N) && (dlt < p.w2) && (kb >= 0);
+                const int ic = min(i, p.N - 1), kc = max(kb, 0);
+                const __nv_bfloat16* q_row = q + ri.b * p.q.b + (long)ic * p.q.n + ri.h * p.q.h;
+                const __nv_bfloat16* do_row = d_o + ri.b * p.d_o.b + (long)ic * p.d_o.n + ri.h * p.d_o.h;
+                const __nv_bfloat16* k2_row = k2 + ri.b * p.k2.b + (long)kc * p.k2.n + ri.hk * p.k2.h;
+                const __nv_bfloat16* v2_row = v2 + ri.b * p.v2.b + (long)kc * p.v2.n + ri.hk * p.v2.h;
+                // ---- stationary operand of this group
+                if (grp == 0) form_row<HD>(my_tile, L::kBigSlab, row, row_valid, q_row, k2_row, p.k2_bias);
+                else form_row<HD>(my_tile, L::kBigSlab, row, row_valid, do_row, v2_row, p.v2_bias);
+                fence_proxy_async_smem();
+                tc_fence_before();
+                mbar_arrive(B.stat_full);
+                const long li = ((long)ri.b * p.H + ri.h) * p.N + ic;
+                const float lse2 = P.lse2[li], dlt_i = P.delta[li];
+                const int jhi = row_valid ? i + p.halo1 : -1;
+                const int jlo = row_valid ? max(0, i + p.halo1 - p.w1 + 1) : 0;
+                // ---- column tiles of this group
+                for (int t = grp; t < ru.nt; t += 2, ++n_mine) {
+                    const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
+                    const int tile0 = ru.col_start + t * kStreamRows;
+                    const int lo = jlo - tile0, hi = jhi - tile0;
+                    const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= kStreamRows - 1);
+                    mbar_wait(&B.sdp_ready[grp], n_mine & 1, wctx, 30);
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c0 = 0; c0 < width; c0 += 32) {
+                        uint32_t s[32], dp[32], pp[16], ds[16];
+                        tmem_ld32(tm_s[grp] + lane_addr + c0, s);
+                        tmem_ld32(tm_dp[grp] + lane_addr + c0, dp);
+                        tmem_wait_ld();
+                        if (full) softmax_bwd_chunk<false>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
+                        else softmax_bwd_chunk<true>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
+                        tmem_st16(tm_s[grp] + lane_addr + (c0 >> 1), pp);
+                        tmem_st16(tm_dp[grp] + lane_addr + (c0 >> 1), ds);
+                    }
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(&B.pds_ready[grp]);
+                }
+                // ---- epilogue: group 0 takes G (dQ and dK2 partials), group 1 takes U (dV2 partials)
+                mbar_wait(B.acc_ready, n_units & 1, wctx, 31);
+                tc_fence_after();
+                const uint32_t acc = (grp == 0 ? tm_g : tm_u) + lane_addr;
+                const __nv_bfloat16* y_row = grp == 0 ? q_row : do_row;
+                const float mult = grp == 0 ? p.scale : 1.f;
+                float* ws_full = grp == 0 ? P.ws_full_k2 : P.ws_full_v2;
+                float* ws_head = grp == 0 ? P.ws_head_k2 : P.ws_head_v2;
+                const int kb_base = i0 + p.halo2 - (DW - 1);                 // K2 buffer row of kbrel = 0
+                const int kb_min = max(0, i0 + p.halo2 - (p.w2 - 1));        // first row any valid delta reaches
+                const int kb_max = min(i0 + qpt, p.N) - 1 + p.halo2;
+                const int own0 = ri.i_run0 + p.halo2;                        // first row owned by this run
+#pragma unroll 1
+                for (int c = 0; c < HD / CW; ++c) {
+                    uint32_t g[CW];
+                    tmem_ld_cw<CW>(acc + c * CW, g);
+                    float y[CW];
+                    load_bf16_cw<CW>(y_row, c * CW, 0.f, y);
+                    if (grp == 0) {
+                        float x[CW];
+                        load_bf16_cw<CW>(k2_row, c * CW, p.k2_bias, x);
+#pragma unroll
+                        for (int e = 0; e < CW; ++e)
+                            scr_a[row * CW + (e ^ (row & (CW - 1)))] = row_valid ? __uint_as_float(g[e]) * x[e] * mult : 0.f;
+                    }
+#pragma unroll
+                    for (int e = 0; e < CW; ++e)
+                        scr_b[row * CW + (e ^ (row & (CW - 1)))] = row_valid ? __uint_as_float(g[e]) * y[e] * mult : 0.f;
+                    named_barrier_sync(1 + grp, 128);
+                    if (grp == 0 && dq != nullptr) {
+                        for (int idx = row; idx < qpt * CW; idx += 128) {
+                            const int q2 = idx / CW, e = idx % CW;
+                            float a = 0.f;
+                            for (int d2 = 0; d2 < DW; ++d2) {
+                                const int rr = (q2 << P.dw_log2) + d2;
+                                a += scr_a[rr * CW + (e ^ (rr & (CW - 1)))];
+                            }
+                            if (i0 + q2 < p.N)
+                                dq[ri.b * p.dq.b + (long)(i0 + q2) * p.dq.n + ri.h * p.dq.h + c * CW + e] = __float2bfloat16_rn(a);
+                        }
+                    }
+                    if (need_kv2) {
+                        const int nrows = DW + qpt - 1;
+                        for (int idx = row; idx < nrows * CW; idx += 128) {
+                            const int kbrel = idx / CW, e = idx % CW;
+                            const int kbt = kb_base + kbrel;
+                            if (kbt < kb_min || kbt > kb_max) continue;
+                            float a = 0.f;
+                            for (int q2 = 0; q2 < qpt; ++q2) {
+                                const int d2 = q2 + DW - 1 - kbrel;
+                                if (d2 >= 0 && d2 < DW) {
+                                    const int rr = (q2 << P.dw_log2) + d2;
+                                    a += scr_b[rr * CW + (e ^ (rr & (CW - 1)))];
+                                }
+                            }
+                            float* dst;
+                            bool first;
+                            if (kbt >= own0) {
+                                dst = ws_full + (((long)ri.b * p.H + ri.h) * p.N + (kbt - p.halo2)) * HD + c * CW + e;
+                                first = kbt >= i0 + p.halo2;
+                            } else {
+                                const int slot = kbt - (own0 - (p.w2 - 1));
+                                dst = ws_head + ((((long)ri.b * p.H + ri.h) * P.num_runs + ri.run) * (p.w2 - 1) + slot) * HD + c * CW + e;
+                                first = uidx == 0;
+                            }
+                            *dst = first ? a : *dst + a;
+                        }
+                    }
+                    named_barrier_sync(1 + grp, 128);
+                }
+                tc_fence_before();
+                mbar_arrive(B.acc_free);
+            }
+        }
+    } else if (warp == 12) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            uint32_t nb[2] = {0, 0}, g_base = 0, n_units = 0;
+            const uint32_t a_s = smem_base + L::kStat0, c_s = smem_base + L::kStat1;
+            for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
+                const RowItem ri = row_item(P, it);
+                for (int i0 = ri.i_run0; i0 < ri.i_run1; i0 += qpt, ++n_units) {
+                    const RowUnit ru = row_unit(P, i0);
+                    mbar_wait(B.stat_full, n_units & 1, wctx, 32);      // A, C formed (implies last epilogue done)
+                    tc_fence_after();
+                    for (int t = 0; t <= ru.nt; ++t) {
+                        if (t < ru.nt) {
+                            const uint32_t g = g_base + t;
+                            const int stage = (int)(g % kBwdStages), b = t & 1;
+                            const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
+                            const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
+                            mbar_wait(&B.st_full[stage], (g / kBwdStages) & 1, wctx, 33);
+                            tc_fence_after();
+                            issue_sdp<HD>(tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width);
+                            tc_commit(&B.sdp_ready[b]);
+                        }
+                        if (t >= 1) {
+                            const int tp = t - 1;
+                            const uint32_t g = g_base + tp;
+                            const int stage = (int)(g % kBwdStages), b = tp & 1;
+                            const int width = (tp == ru.nt - 1) ? ru.last_width : kStreamRows;
+                            const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
+                            mbar_wait(&B.pds_ready[b], nb[b] & 1, wctx, 34);
+                            ++nb[b];
+                            tc_fence_after();
+                            // U += P V1-tile ; G += dS K1-tile
+                            issue_acc<HD>(tm_u, tm_g, tm_s[b], tm_dp[b], k1_t, v1_t, width, tp > 0);
+                            tc_commit(&B.st_empty[stage]);
+                        }
+                    }
+                    tc_commit(B.acc_ready);
+                    g_base += ru.nt;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 13) {
+        // ---------------------------------------------------------------- TMA: streamed K1 / V1 tiles
+        if (lane == 0) {
+            prefetch_tensormap(&map_k1);
+            prefetch_tensormap(&map_v1);
+            uint32_t g = 0;
+            for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
+                const RowItem ri = row_item(P, it);
+                for (int i0 = ri.i_run0; i0 < ri.i_run1; i0 += qpt) {
+                    const RowUnit ru = row_unit(P, i0);
+                    for (int t = 0; t < ru.nt; ++t, ++g) {
+                        const int stage = (int)(g % kBwdStages);
+                        const int r0 = ru.col_start + t * kStreamRows;
+                        uint8_t* k1_t = smem + L::kStream + stage * 2 * L::kSmallTile;
+                        uint8_t* v1_t = k1_t + L::kSmallTile;
+                        mbar_wait(&B.st_empty[stage], ((g / kBwdStages) & 1) ^ 1, wctx, 35);
+                        mbar_arrive_expect_tx(&B.st_full[stage], 2 * L::kSmallTile);
+#pragma unroll
+                        for (int sl = 0; sl < L::kSlabs; ++sl) {
+                            tma_load_4d(k1_t + sl * L::kSmallSlab, &map_k1, &B.st_full[stage], sl * 64, r0, ri.hk, ri.b);
+                            tma_load_4d(v1_t + sl * L::kSmallSlab, &map_v1, &B.st_full[stage], sl * 64, r0, ri.hk, ri.b);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 12) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// 4. dK2 / dV2 from the fp32 partials: sum over the query heads of a group, add the head partials of
+//    the runs that start within w2-1 queries after the row, convert to bf16.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+kv2_reduce_kernel(BwdTcParams P, __nv_bfloat16* __restrict__ dk2, __nv_bfloat16* __restrict__ dv2) {
+    const KParams& p = P.k;
+    const int HD = p.D;
+    const long total = (long)p.B * p.n2 * p.Hkv * (HD / 2);
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int d = (int)(idx % (HD / 2)) * 2;
+    const int hk = (int)((idx / (HD / 2)) % p.Hkv);
+    const int kb = (int)((idx / (HD / 2) / p.Hkv) % p.n2);
+    const int b = (int)(idx / (HD / 2) / p.Hkv / p.n2);
+    const int runq = P.units_per_run * (128 >> P.dw_log2);
+    const int ip = kb - p.halo2;                          // the query aligned with this row (may be negative)
+    // runs r with  r*runq in [ip + 1, ip + w2 - 1]
+    int r_lo = (ip + 1 <= 0) ? 0 : (ip + 1 + runq - 1) / runq;
+    int r_hi = (ip + p.w2 - 1 < 0) ? -1 : (ip + p.w2 - 1) / runq;
+    if (r_hi > P.num_runs - 1) r_hi = P.num_runs - 1;
+    float2 ak = make_float2(0.f, 0.f), av = make_float2(0.f, 0.f);
+    for (int hq = 0; hq < p.G; ++hq) {
+        const int h = hk * p.G + hq;
+        const long bh = (long)b * p.H + h;
+        if (ip >= 0 && ip < p.N) {
+            const long o = (bh * p.N + ip) * HD + d;
+            if (dk2) { const float2 t = *(const float2*)(P.ws_full_k2 + o); ak.x += t.x; ak.y += t.y; }
+            if (dv2) { const float2 t = *(const float2*)(P.ws_full_v2 + o); av.x += t.x; av.y += t.y; }
+        }
+        for (int r = r_lo; r <= r_hi; ++r) {
+            const int slot = kb - (r * runq + p.halo2 - (p.w2 - 1));
+            const long o = ((bh * P.num_runs + r) * (p.w2 - 1) + slot) * HD + d;
+            if (dk2) { const float2 t = *(const float2*)(P.ws_head_k2 + o); ak.x += t.x; ak.y += t.y; }
+            if (dv2) { const float2 t = *(const float2*)(P.ws_head_v2 + o); av.x += t.x; av.y += t.y; }
+        }
+    }
+    if (dk2) *(__nv_bfloat162*)(dk2 + b * p.dk2.b + (long)kb * p.dk2.n + hk * p.dk2.h + d) = __floats2bfloat162_rn(ak.x, ak.y);
+    if (dv2) *(__nv_bfloat162*)(dv2 + b * p.dv2.b + (long)kb * p.dv2.n + hk * p.dv2.h + d) = __floats2bfloat162_rn(av.x, av.y);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+struct BwdPlan {
+    int dw_log2, qpt, units_per_run, num_runs;
+    size_t off_lse2, off_delta, off_full_k2, off_full_v2, off_head_k2, off_head_v2, total;
+};
+
+inline BwdPlan bwd_plan(const KParams& k) {
+    BwdPlan pl{};
+    int l = 0;
+    while ((1 << l) < k.w2) ++l;
+    pl.dw_log2 = l;
+    pl.qpt = 128 >> l;
+    const int units = (k.N + pl.qpt - 1) / pl.qpt;
+    int upr = 16;
+    while (upr > 1 && (long)k.B * k.H * ((units + upr - 1) / upr) < 2 * 148) upr >>= 1;
+    pl.units_per_run = upr;
+    pl.num_runs = (units + upr - 1) / upr;
+    auto align = [](size_t x) { return (x + 255) & ~(size_t)255; };
+    const size_t bhn = (size_t)k.B * k.H * k.N;
+    size_t off = 0;
+    pl.off_lse2 = off; off = align(off + bhn * 4);
+    pl.off_delta = off; off = align(off + bhn * 4);
+    pl.off_full_k2 = off; off = align(off + bhn * k.D * 4);
+    pl.off_full_v2 = off; off = align(off + bhn * k.D * 4);
+    const size_t head = (size_t)k.B * k.H * pl.num_runs * (size_t)(k.w2 > 1 ? k.w2 - 1 : 1) * k.D * 4;
+    pl.off_head_k2 = off; off = align(off + head);
+    pl.off_head_v2 = off; off = align(off + head);
+    pl.total = off;
+    return pl;
+}
+
+inline size_t bwd_workspace_bytes(const KParams& k) { return bwd_plan(k).total; }
+
+typedef bool (*MakeMapFn)(CUtensorMap*, const void*, int, int, int, int, const sa_strides&, int);
 
 // Returns an sa_status, or -1 when the tensor-core backward does not cover the problem.
 inline int launch_bwd(const KParams& k, const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
                       const void* o, const float* lse, const void* d_o, void* dq, void* dk1, void* dk2, void* dv1,
-                      void* dv2, uint8_t* workspace, DeviceStatus* status, cudaStream_t st, int* nlaunch) {
-    return -1;
+                      void* dv2, uint8_t* workspace, DeviceStatus* status, cudaStream_t st, int* nlaunch, MakeMapFn make_map,
+                      int sm_count) {
+    const BwdPlan pl = bwd_plan(k);
+    BwdTcParams P{};
+    P.k = k;
+    P.dw_log2 = pl.dw_log2;
+    P.num_jtiles = (k.n1 + 127) / 128;
+    P.num_col_items = (long)k.B * k.Hkv * P.num_jtiles;
+    P.units_per_run = pl.units_per_run;
+    P.num_runs = pl.num_runs;
+    P.num_row_items = (long)k.B * k.H * pl.num_runs;
+    float* lse2 = (float*)(workspace + pl.off_lse2);
+    float* delta = (float*)(workspace + pl.off_delta);
+    P.lse2 = lse2;
+    P.delta = delta;
+    P.ws_full_k2 = (float*)(workspace + pl.off_full_k2);
+    P.ws_full_v2 = (float*)(workspace + pl.off_full_v2);
+    P.ws_head_k2 = (float*)(workspace + pl.off_head_k2);
+    P.ws_head_v2 = (float*)(workspace + pl.off_head_v2);
+    P.status = status;
+    auto bf = [](const void* x) { return (const __nv_bfloat16*)x; };
+
+    const long rows = (long)k.B * k.H * k.N;
+    prep_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(k, bf(o), bf(d_o), lse, lse2, delta);
+    ++*nlaunch;
+
+    if (dk1 || dv1) {
+        CUtensorMap m1, m2;
+        if (!make_map(&m1, k1, k.B, k.n1, k.Hkv, k.D, k.k1, 128)) return SA_ERR_BAD_STRIDE;
+        if (!make_map(&m2, v1, k.B, k.n1, k.Hkv, k.D, k.v1, 128)) return SA_ERR_BAD_STRIDE;
+        const long grid = P.num_col_items < sm_count ? P.num_col_items : sm_count;
+        if (k.D == 128) {
+            auto kern = bwd_col_kernel<128>;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<128>::kAlloc) != cudaSuccess)
+                return SA_ERR_LAUNCH;
+            kern<<<(unsigned)grid, kBwdThreads, BwdSmem<128>::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
+                                                                             (__nv_bfloat16*)dk1, (__nv_bfloat16*)dv1);
+        } else {
+            auto kern = bwd_col_kernel<64>;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<64>::kAlloc) != cudaSuccess)
+                return SA_ERR_LAUNCH;
+            kern<<<(unsigned)grid, kBwdThreads, BwdSmem<64>::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
+                                                                            (__nv_bfloat16*)dk1, (__nv_bfloat16*)dv1);
+        }
+        ++*nlaunch;
+    }
+    if (dq || dk2 || dv2) {
+        CUtensorMap m1, m2;
+        if (!make_map(&m1, k1, k.B, k.n1, k.Hkv, k.D, k.k1, kStreamRows)) return SA_ERR_BAD_STRIDE;
+        if (!make_map(&m2, v1, k.B, k.n1, k.Hkv, k.D, k.v1, kStreamRows)) return SA_ERR_BAD_STRIDE;
+        const long grid = P.num_row_items < sm_count ? P.num_row_items : sm_count;
+        const int need_kv2 = (dk2 || dv2) ? 1 : 0;
+        if (k.D == 128) {
+            auto kern = bwd_row_kernel<128>;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<128>::kAlloc) != cudaSuccess)
+                return SA_ERR_LAUNCH;
+            kern<<<(unsigned)grid, kBwdThreads, BwdSmem<128>::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
+                                                                             (__nv_bfloat16*)dq, need_kv2);
+        } else {
+            auto kern = bwd_row_kernel<64>;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<64>::kAlloc) != cudaSuccess)
+                return SA_ERR_LAUNCH;
+            kern<<<(unsigned)grid, kBwdThreads, BwdSmem<64>::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
+                                                                            (__nv_bfloat16*)dq, need_kv2);
+        }
+        ++*nlaunch;
+        if (need_kv2) {
+            const long total = (long)k.B * k.n2 * k.Hkv * (k.D / 2);
+            kv2_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(P, (__nv_bfloat16*)dk2, (__nv_bfloat16*)dv2);
+            ++*nlaunch;
+        }
+    }
+    return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
 }
 
 }  // namespace tc

@@ -21,7 +21,7 @@ TOL_O_BF16 = 2e-2
 TOL_G_BF16 = 1e-2
 TOL_F32 = 1e-4
 DEV = "cuda"
-TC_BWD_READY = False     # until the tensor-core backward lands, its tests run the general backward
+TC_BWD_READY = True
 
 
 def _grad_err(a, b):
