@@ -235,6 +235,78 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+
+// Product of two bf16 chunks of 8 elements, x * (y + bias), computed in fp32 and rounded once.
+__device__ __forceinline__ uint4 mul_chunk(const uint4& xa, const uint4& ya, float bias) {
+    const __nv_bfloat162* xh = (const __nv_bfloat162*)&xa;
+    const __nv_bfloat162* yh = (const __nv_bfloat162*)&ya;
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 xf = __bfloat1622float2(xh[e]);
+        const float2 yf = __bfloat1622float2(yh[e]);
+        w[e] = pack_bf16(xf.x * (yf.x + bias), xf.y * (yf.y + bias));
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Forms `nrows` rows of a 128-byte-swizzled operand tile ([nrows x 64] slabs, `slab_bytes` apart)
+// with `nthreads` cooperating threads (`t` = index of this thread among them).  Tile row r is the
+// virtual row rho = rho0 + r:  i = rho >> dw_log2,  delta = rho & (DW-1),  kb = i + halo2 - delta,
+//     row = x[i, :] * (y[kb, :] + bias)          (zeros when i >= n_q, delta >= w2 or kb < 0)
+// where x and y point at row 0 of the right batch and head and have row strides xs, ys (elements).
+// Consecutive threads take consecutive 16-byte chunks of a row, so global loads coalesce and the
+// shared-memory stores of a quarter warp hit eight distinct 16-byte slots of one 128-byte line.
+// With bias == 0 the product of two bf16 values rounded to bf16 is exactly what the packed bf16
+// multiply returns (the product of two 8-bit significands is exact in fp32, one rounding follows).
+__device__ __forceinline__ uint4 mul_chunk_nobias(const uint4& xa, const uint4& ya) {
+    uint4 r;
+    const __nv_bfloat162* xh = (const __nv_bfloat162*)&xa;
+    const __nv_bfloat162* yh = (const __nv_bfloat162*)&ya;
+    __nv_bfloat162* rh = (__nv_bfloat162*)&r;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) rh[e] = __hmul2(xh[e], yh[e]);
+    return r;
+}
+
+template <int HD, int NROWS, int NTHREADS>
+__device__ __forceinline__ void form_product_tile(uint8_t* tile, int slab_bytes, int t, long rho0, int dw_log2, int n_q,
+                                                  int w2, int halo2, const __nv_bfloat16* x, int64_t xs,
+                                                  const __nv_bfloat16* y, int64_t ys, float bias) {
+    constexpr int C = HD / 8;
+    constexpr int RPP = NTHREADS / C;            // rows per pass
+    constexpr int PASSES = NROWS / RPP;
+    static_assert(NROWS % RPP == 0, "tile rows must be a multiple of the rows formed per pass");
+    constexpr int BATCH = PASSES < 4 ? PASSES : 4;    // loads in flight per thread: 2 * BATCH 16-byte loads
+    static_assert(PASSES % BATCH == 0, "passes must split into whole batches");
+    const int c = t % C;
+    const int dmask = (1 << dw_log2) - 1;
+#pragma unroll 1
+    for (int k0 = 0; k0 < PASSES; k0 += BATCH) {
+        uint4 xa[BATCH], ya[BATCH];
+        bool ok[BATCH];
+#pragma unroll
+        for (int k = 0; k < BATCH; ++k) {         // loads first: one memory round trip per batch
+            const long rho = rho0 + t / C + (k0 + k) * RPP;
+            const int i = (int)(rho >> dw_log2);
+            const int dlt = (int)(rho & dmask);
+            const int kb = i + halo2 - dlt;
+            ok[k] = i < n_q && dlt < w2 && kb >= 0;
+            if (ok[k]) {
+                xa[k] = ((const uint4*)(x + (int64_t)i * xs))[c];
+                ya[k] = ((const uint4*)(y + (int64_t)kb * ys))[c];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < BATCH; ++k) {
+            const int r = t / C + (k0 + k) * RPP;
+            uint4 out = make_uint4(0, 0, 0, 0);
+            if (ok[k]) out = (bias == 0.f) ? mul_chunk_nobias(xa[k], ya[k]) : mul_chunk(xa[k], ya[k], bias);
+            *(uint4*)(tile + (c >> 3) * slab_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = out;
+        }
+    }
+}
+
 // Byte offset of element (row, col) inside a 128-byte-swizzled [rows x 64] bf16 slab.
 __device__ __forceinline__ uint32_t swz128_offset(int row, int col) {
     return (uint32_t)row * 128u + ((((uint32_t)col >> 3) ^ ((uint32_t)row & 7u)) << 4) + (((uint32_t)col & 7u) << 1);

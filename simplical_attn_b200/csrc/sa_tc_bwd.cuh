@@ -36,7 +36,8 @@
 namespace sa {
 namespace tc {
 
-constexpr int kBwdThreads = 512;
+constexpr int kBwdThreads = 512;      // column kernel: 2 softmax groups, producer group, MMA and TMA warps
+constexpr int kRowThreads = 320;      // row kernel: 2 softmax groups, MMA warp (8), TMA warp (9)
 constexpr int kStreamRows = 64;        // rows of a streamed tile = columns of an S / dP tile
 constexpr int kBwdStages = 3;          // streamed-tile ring depth
 
@@ -74,7 +75,9 @@ struct BwdSmem {
     static constexpr int kNumBars = 2 * kBwdStages + 10;
     static constexpr int kMisc = kBars + kNumBars * 8;
     static constexpr int kTotal = kMisc + 16;
+    static constexpr int kRing = kTotal;                     // row kernel: 2 x ring_rows x HD floats (optional)
     static constexpr int kAlloc = (kTotal + 1024 > 120 * 1024) ? kTotal + 1024 : 120 * 1024;
+    static constexpr int kMaxDynamic = 227 * 1024;
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -102,33 +105,6 @@ prep_kernel(KParams p, const __nv_bfloat16* __restrict__ o, const __nv_bfloat16*
     if (lane == 0) {
         delta[row] = s;
         lse2[row] = lse[row] * kLog2e;
-    }
-}
-
-// Product of two bf16 rows (x * (y + bias)), 8 elements per 16-byte chunk, rounded once to bf16.
-__device__ __forceinline__ uint4 mul_chunk(const uint4& xa, const uint4& ya, float bias) {
-    const __nv_bfloat162* xh = (const __nv_bfloat162*)&xa;
-    const __nv_bfloat162* yh = (const __nv_bfloat162*)&ya;
-    uint32_t w[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-        const float2 xf = __bfloat1622float2(xh[e]);
-        const float2 yf = __bfloat1622float2(yh[e]);
-        w[e] = ptx::pack_bf16(xf.x * (yf.x + bias), xf.y * (yf.y + bias));
-    }
-    return make_uint4(w[0], w[1], w[2], w[3]);
-}
-
-// Writes row `row` of a 128-byte-swizzled tile made of [rows x 64] slabs `slab_bytes` apart:
-// out = x * (y + bias) over HD elements, or zeros.
-template <int HD>
-__device__ __forceinline__ void form_row(uint8_t* tile, int slab_bytes, int row, bool valid, const __nv_bfloat16* x,
-                                         const __nv_bfloat16* y, float bias) {
-#pragma unroll
-    for (int c = 0; c < HD / 8; ++c) {
-        uint4 out = make_uint4(0, 0, 0, 0);
-        if (valid) out = mul_chunk(((const uint4*)x)[c], ((const uint4*)y)[c], bias);
-        *(uint4*)(tile + (c >> 3) * slab_bytes + row * 128 + (((c & 7) ^ (row & 7)) << 4)) = out;
     }
 }
 
@@ -377,8 +353,6 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     } else if (warp < 12) {
         // ---------------------------------------------------------------- producer of the A / C tiles
         const int ptid = tid - 256;
-        const int prow = ptid & 63;
-        const int which = ptid >> 6;                      // 0: A = Q * K2, 1: C = dO * V2
         uint32_t g_base = 0;
         for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
             const ColItem ci = col_item(P, it);
@@ -387,28 +361,24 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const uint32_t g = g_base + t;
                 const int stage = (int)(g % kBwdStages);
                 const int h = ci.hk * p.G + t / ci.ntq;
-                const int tt = ci.tt_lo + (t % ci.ntq);
-                const long rho = (long)tt * kStreamRows + prow;
-                const int i = (int)(rho >> P.dw_log2);
-                const int dlt = (int)(rho & (DW - 1));
-                const int kb = i + p.halo2 - dlt;
-                const bool valid = (i < p.N) && (dlt < p.w2) && (kb >= 0);
-                const int ic = min(i, p.N - 1), kc = max(kb, 0);
+                const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kStreamRows;
                 mbar_wait(&B.st_empty[stage], ((g / kBwdStages) & 1) ^ 1, wctx, 22);
-                uint8_t* tile = smem + L::kStream + stage * 2 * L::kSmallTile + which * L::kSmallTile;
-                if (which == 0) {
-                    form_row<HD>(tile, L::kSmallSlab, prow, valid, q + ci.b * p.q.b + (long)ic * p.q.n + h * p.q.h,
-                                 k2 + ci.b * p.k2.b + (long)kc * p.k2.n + ci.hk * p.k2.h, p.k2_bias);
-                    if (prow == 0 || dlt == 0) {
-                        const int qidx = i - (int)(((long)tt * kStreamRows) >> P.dw_log2);
-                        float* m_lse = (float*)(smem + L::kMeta) + stage * 128;
-                        const long li = ((long)ci.b * p.H + h) * p.N + ic;
-                        m_lse[qidx] = (i < p.N) ? P.lse2[li] : INFINITY;
-                        m_lse[64 + qidx] = (i < p.N) ? P.delta[li] : 0.f;
-                    }
-                } else {
-                    form_row<HD>(tile, L::kSmallSlab, prow, valid, d_o + ci.b * p.d_o.b + (long)ic * p.d_o.n + h * p.d_o.h,
-                                 v2 + ci.b * p.v2.b + (long)kc * p.v2.n + ci.hk * p.v2.h, p.v2_bias);
+                uint8_t* a_tile = smem + L::kStream + stage * 2 * L::kSmallTile;
+                form_product_tile<HD, kStreamRows, 128>(a_tile, L::kSmallSlab, ptid, rho0, P.dw_log2, p.N, p.w2, p.halo2,
+                                      q + ci.b * p.q.b + h * p.q.h, p.q.n, k2 + ci.b * p.k2.b + ci.hk * p.k2.h, p.k2.n,
+                                      p.k2_bias);
+                form_product_tile<HD, kStreamRows, 128>(a_tile + L::kSmallTile, L::kSmallSlab, ptid, rho0, P.dw_log2, p.N, p.w2,
+                                      p.halo2, d_o + ci.b * p.d_o.b + h * p.d_o.h, p.d_o.n,
+                                      v2 + ci.b * p.v2.b + ci.hk * p.v2.h, p.v2.n, p.v2_bias);
+                // LSE2 and Delta of the tile's queries
+                const int iq0 = (int)(rho0 >> P.dw_log2);
+                const int nq = max(1, kStreamRows >> P.dw_log2);
+                if (ptid < nq) {
+                    const int i = iq0 + ptid;
+                    float* m_lse = (float*)(smem + L::kMeta) + stage * 128;
+                    const long li = ((long)ci.b * p.H + h) * p.N + min(i, p.N - 1);
+                    m_lse[ptid] = (i < p.N) ? P.lse2[li] : INFINITY;
+                    m_lse[64 + ptid] = (i < p.N) ? P.delta[li] : 0.f;
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(&B.st_full[stage]);
@@ -552,11 +522,11 @@ __device__ __forceinline__ void load_bf16_cw(const __nv_bfloat16* row, int col, 
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kRowThreads, 1)
 bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
                const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
                const __nv_bfloat16* __restrict__ k2, const __nv_bfloat16* __restrict__ v2,
-               const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dq, int need_kv2) {
+               const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dq, int need_kv2, int ring_rows) {
     using L = BwdSmem<HD>;
     using namespace ptx;
     constexpr int CW = HD / 4;                            // epilogue chunk width
@@ -586,7 +556,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 12) {
+    if (warp == 8) {
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
@@ -611,6 +581,12 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         uint8_t* my_tile = smem + (grp == 0 ? L::kStat0 : L::kStat1);      // group 0 forms A, group 1 forms C
         float* scr_a = (float*)my_tile;                   // [128][CW] fp32, column index XOR-swizzled by the row
         float* scr_b = scr_a + 128 * CW;
+        // fp32 accumulators of the dK2 (group 0) / dV2 (group 1) rows currently within reach of the
+        // block's queries, one slot per row modulo ring_rows; ring_rows == 0: not enough shared memory
+        float* ring = (float*)(smem + L::kRing) + grp * ring_rows * HD;
+        for (int x = row; x < ring_rows * HD; x += 128) ring[x] = 0.f;
+        named_barrier_sync(1 + grp, 128);
+        int flush_lo = 0;
         uint32_t n_mine = 0, n_units = 0;
         for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
             const RowItem ri = row_item(P, it);
@@ -625,8 +601,14 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const __nv_bfloat16* k2_row = k2 + ri.b * p.k2.b + (long)kc * p.k2.n + ri.hk * p.k2.h;
                 const __nv_bfloat16* v2_row = v2 + ri.b * p.v2.b + (long)kc * p.v2.n + ri.hk * p.v2.h;
                 // ---- stationary operand of this group
-                if (grp == 0) form_row<HD>(my_tile, L::kBigSlab, row, row_valid, q_row, k2_row, p.k2_bias);
-                else form_row<HD>(my_tile, L::kBigSlab, row, row_valid, do_row, v2_row, p.v2_bias);
+                if (grp == 0)
+                    form_product_tile<HD, 128, 128>(my_tile, L::kBigSlab, row, (long)i0 << P.dw_log2, P.dw_log2, p.N, p.w2, p.halo2,
+                                          q + ri.b * p.q.b + ri.h * p.q.h, p.q.n, k2 + ri.b * p.k2.b + ri.hk * p.k2.h, p.k2.n,
+                                          p.k2_bias);
+                else
+                    form_product_tile<HD, 128, 128>(my_tile, L::kBigSlab, row, (long)i0 << P.dw_log2, P.dw_log2, p.N, p.w2, p.halo2,
+                                          d_o + ri.b * p.d_o.b + ri.h * p.d_o.h, p.d_o.n,
+                                          v2 + ri.b * p.v2.b + ri.hk * p.v2.h, p.v2.n, p.v2_bias);
                 fence_proxy_async_smem();
                 tc_fence_before();
                 mbar_arrive(B.stat_full);
@@ -658,33 +640,49 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     mbar_arrive(&B.pds_ready[grp]);
                 }
                 // ---- epilogue: group 0 takes G (dQ and dK2 partials), group 1 takes U (dV2 partials)
-                mbar_wait(B.acc_ready, n_units & 1, wctx, 31);
-                tc_fence_after();
                 const uint32_t acc = (grp == 0 ? tm_g : tm_u) + lane_addr;
                 const __nv_bfloat16* y_row = grp == 0 ? q_row : do_row;
                 const float mult = grp == 0 ? p.scale : 1.f;
                 float* ws_full = grp == 0 ? P.ws_full_k2 : P.ws_full_v2;
                 float* ws_head = grp == 0 ? P.ws_head_k2 : P.ws_head_v2;
+                const long bh = (long)ri.b * p.H + ri.h;
                 const int kb_base = i0 + p.halo2 - (DW - 1);                 // K2 buffer row of kbrel = 0
                 const int kb_min = max(0, i0 + p.halo2 - (p.w2 - 1));        // first row any valid delta reaches
                 const int kb_max = min(i0 + qpt, p.N) - 1 + p.halo2;
                 const int own0 = ri.i_run0 + p.halo2;                        // first row owned by this run
-#pragma unroll 1
+                if (uidx == 0) flush_lo = max(0, own0 - (p.w2 - 1));
+                // the factors of this thread's row, fetched one chunk ahead of their use
+                uint4 yraw[2][CW / 8], xraw[2][CW / 8];
+#pragma unroll
+                for (int x = 0; x < CW / 8; ++x) {
+                    yraw[0][x] = ((const uint4*)y_row)[x];
+                    if (grp == 0) xraw[0][x] = ((const uint4*)k2_row)[x];
+                }
+                mbar_wait(B.acc_ready, n_units & 1, wctx, 31);
+                tc_fence_after();
+#pragma unroll
                 for (int c = 0; c < HD / CW; ++c) {
                     uint32_t g[CW];
                     tmem_ld_cw<CW>(acc + c * CW, g);
-                    float y[CW];
-                    load_bf16_cw<CW>(y_row, c * CW, 0.f, y);
+                    if (c + 1 < HD / CW) {
+#pragma unroll
+                        for (int x = 0; x < CW / 8; ++x) {
+                            yraw[(c + 1) & 1][x] = ((const uint4*)(y_row + (c + 1) * CW))[x];
+                            if (grp == 0) xraw[(c + 1) & 1][x] = ((const uint4*)(k2_row + (c + 1) * CW))[x];
+                        }
+                    }
+                    const __nv_bfloat16* yh = (const __nv_bfloat16*)yraw[c & 1];
+                    const __nv_bfloat16* xh = (const __nv_bfloat16*)xraw[c & 1];
                     if (grp == 0) {
-                        float x[CW];
-                        load_bf16_cw<CW>(k2_row, c * CW, p.k2_bias, x);
 #pragma unroll
                         for (int e = 0; e < CW; ++e)
-                            scr_a[row * CW + (e ^ (row & (CW - 1)))] = row_valid ? __uint_as_float(g[e]) * x[e] * mult : 0.f;
+                            scr_a[row * CW + (e ^ (row & (CW - 1)))] =
+                                row_valid ? __uint_as_float(g[e]) * (__bfloat162float(xh[e]) + p.k2_bias) * mult : 0.f;
                     }
 #pragma unroll
                     for (int e = 0; e < CW; ++e)
-                        scr_b[row * CW + (e ^ (row & (CW - 1)))] = row_valid ? __uint_as_float(g[e]) * y[e] * mult : 0.f;
+                        scr_b[row * CW + (e ^ (row & (CW - 1)))] =
+                            row_valid ? __uint_as_float(g[e]) * __bfloat162float(yh[e]) * mult : 0.f;
                     named_barrier_sync(1 + grp, 128);
                     if (grp == 0 && dq != nullptr) {
                         for (int idx = row; idx < qpt * CW; idx += 128) {
@@ -712,26 +710,46 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                                     a += scr_b[rr * CW + (e ^ (rr & (CW - 1)))];
                                 }
                             }
-                            float* dst;
-                            bool first;
-                            if (kbt >= own0) {
-                                dst = ws_full + (((long)ri.b * p.H + ri.h) * p.N + (kbt - p.halo2)) * HD + c * CW + e;
-                                first = kbt >= i0 + p.halo2;
+                            if (ring_rows > 0) {
+                                ring[(kbt % ring_rows) * HD + c * CW + e] += a;
                             } else {
-                                const int slot = kbt - (own0 - (p.w2 - 1));
-                                dst = ws_head + ((((long)ri.b * p.H + ri.h) * P.num_runs + ri.run) * (p.w2 - 1) + slot) * HD + c * CW + e;
-                                first = uidx == 0;
+                                // no room for the ring: accumulate in the workspace (this block alone touches the row)
+                                float* dst;
+                                bool first;
+                                if (kbt >= own0) {
+                                    dst = ws_full + (bh * p.N + (kbt - p.halo2)) * HD + c * CW + e;
+                                    first = kbt >= i0 + p.halo2;
+                                } else {
+                                    const int slot = kbt - (own0 - (p.w2 - 1));
+                                    dst = ws_head + ((bh * P.num_runs + ri.run) * (p.w2 - 1) + slot) * HD + c * CW + e;
+                                    first = uidx == 0;
+                                }
+                                *dst = first ? a : *dst + a;
                             }
-                            *dst = first ? a : *dst + a;
                         }
                     }
                     named_barrier_sync(1 + grp, 128);
+                }
+                if (need_kv2 && ring_rows > 0) {
+                    // rows no later query of the run reaches are final: move them to the workspace, clear the slots
+                    const bool last_unit = i0 + qpt >= ri.i_run1;
+                    const int f_hi = last_unit ? kb_max + 1 : max(0, i0 + qpt + p.halo2 - (p.w2 - 1));
+                    for (int kbf = flush_lo; kbf < f_hi; ++kbf) {
+                        float* src = ring + (kbf % ring_rows) * HD;
+                        float* dst = (kbf >= own0) ? ws_full + (bh * p.N + (kbf - p.halo2)) * HD
+                                                   : ws_head + ((bh * P.num_runs + ri.run) * (p.w2 - 1) + (kbf - (own0 - (p.w2 - 1)))) * HD;
+                        for (int d = row; d < HD; d += 128) {
+                            dst[d] = src[d];
+                            src[d] = 0.f;
+                        }
+                    }
+                    flush_lo = max(flush_lo, f_hi);
                 }
                 tc_fence_before();
                 mbar_arrive(B.acc_free);
             }
         }
-    } else if (warp == 12) {
+    } else if (warp == 8) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             uint32_t nb[2] = {0, 0}, g_base = 0, n_units = 0;
@@ -773,7 +791,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
             }
         }
         __syncwarp();
-    } else if (warp == 13) {
+    } else if (warp == 9) {
         // ---------------------------------------------------------------- TMA: streamed K1 / V1 tiles
         if (lane == 0) {
             prefetch_tensormap(&map_k1);
@@ -803,7 +821,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 12) {
+    if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
@@ -942,18 +960,28 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         if (!make_map(&m2, v1, k.B, k.n1, k.Hkv, k.D, k.v1, kStreamRows)) return SA_ERR_BAD_STRIDE;
         const long grid = P.num_row_items < sm_count ? P.num_row_items : sm_count;
         const int need_kv2 = (dk2 || dv2) ? 1 : 0;
+        // shared-memory ring of fp32 dK2/dV2 rows if it fits beside the tiles
+        int ring_rows = (1 << pl.dw_log2) + pl.qpt;
         if (k.D == 128) {
+            using L = BwdSmem<128>;
+            int smem = L::kTotal + 1024 + 2 * ring_rows * 128 * 4;
+            if (!need_kv2 || smem > L::kMaxDynamic) { ring_rows = 0; smem = L::kAlloc; }
+            if (smem < L::kAlloc) smem = L::kAlloc;
             auto kern = bwd_row_kernel<128>;
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<128>::kAlloc) != cudaSuccess)
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kMaxDynamic) != cudaSuccess)
                 return SA_ERR_LAUNCH;
-            kern<<<(unsigned)grid, kBwdThreads, BwdSmem<128>::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
-                                                                             (__nv_bfloat16*)dq, need_kv2);
+            kern<<<(unsigned)grid, kRowThreads, smem, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o), (__nv_bfloat16*)dq,
+                                                            need_kv2, ring_rows);
         } else {
+            using L = BwdSmem<64>;
+            int smem = L::kTotal + 1024 + 2 * ring_rows * 64 * 4;
+            if (!need_kv2 || smem > L::kMaxDynamic) { ring_rows = 0; smem = L::kAlloc; }
+            if (smem < L::kAlloc) smem = L::kAlloc;
             auto kern = bwd_row_kernel<64>;
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<64>::kAlloc) != cudaSuccess)
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kMaxDynamic) != cudaSuccess)
                 return SA_ERR_LAUNCH;
-            kern<<<(unsigned)grid, kBwdThreads, BwdSmem<64>::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
-                                                                            (__nv_bfloat16*)dq, need_kv2);
+            kern<<<(unsigned)grid, kRowThreads, smem, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o), (__nv_bfloat16*)dq,
+                                                            need_kv2, ring_rows);
         }
         ++*nlaunch;
         if (need_kv2) {

@@ -255,32 +255,12 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
             const int i = ug.i0 + r * qpt + qq;
             const int kb = i + p.halo2 - delta;                    // K2/V2 buffer row
             const bool row_valid = (i < p.N) && (delta < p.w2) && (kb >= 0);
-            // ---- form A[row, :] = Q_i * (K2_kb + bias) as bf16, 128-byte swizzled
-            {
-                const uint4* qrow = (const uint4*)(q + ug.b * p.q.b + (long)min(i, p.N - 1) * p.q.n + ug.h * p.q.h);
-                const uint4* krow = (const uint4*)(k2 + ug.b * p.k2.b + (long)max(kb, 0) * p.k2.n + ug.hk * p.k2.h);
-#pragma unroll
-                for (int c = 0; c < HD / 8; ++c) {
-                    uint4 out = make_uint4(0, 0, 0, 0);
-                    if (row_valid) {
-                        const uint4 qa = qrow[c], ka = krow[c];
-                        const __nv_bfloat162* qh = (const __nv_bfloat162*)&qa;
-                        const __nv_bfloat162* kh = (const __nv_bfloat162*)&ka;
-                        uint32_t w[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float2 qf = __bfloat1622float2(qh[e]);
-                            const float2 kf = __bfloat1622float2(kh[e]);
-                            w[e] = pack_bf16(qf.x * (kf.x + p.k2_bias), qf.y * (kf.y + p.k2_bias));
-                        }
-                        out = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
-                    const int slab = c >> 3, cc = c & 7;
-                    *(uint4*)(a_tile + slab * L::kSlabBytes + row * 128 + ((cc ^ (row & 7)) << 4)) = out;
-                }
-                fence_proxy_async_smem();
-                mbar_arrive(&a_ready[r]);
-            }
+            // ---- form A_r: row (i, delta) = Q_i * (K2_{i-delta} + bias) as bf16, 128-byte swizzled
+            form_product_tile<HD, kRowTile, kRowTile>(a_tile, L::kSlabBytes, row, (long)(ug.i0 + r * qpt) << P.dw_log2, P.dw_log2,
+                                  p.N, p.w2, p.halo2, q + ug.b * p.q.b + ug.h * p.q.h, p.q.n,
+                                  k2 + ug.b * p.k2.b + ug.hk * p.k2.h, p.k2.n, p.k2_bias);
+            fence_proxy_async_smem();
+            mbar_arrive(&a_ready[r]);
             // ---- main loop over column tiles
             // Valid buffer rows of this virtual row: [jlo, jhi] (empty for an invalid row).
             const int jhi = row_valid ? i + p.halo1 : -1;
