@@ -177,6 +177,19 @@ int sa_version(void) { return 100; }
 
 uint64_t sa_kernel_launches(void) { return g_launches.load(); }
 
+#ifdef SA_PROFILE
+// Profiling builds only: copies and clears the per-wait-site cycle and hit counters of block 0.
+int sa_prof_read(unsigned long long* cycles, unsigned long long* counts) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(cycles, sa::ptx::g_prof_cycles, 64 * 8);
+    cudaMemcpyFromSymbol(counts, sa::ptx::g_prof_count, 64 * 8);
+    unsigned long long z[64] = {0};
+    cudaMemcpyToSymbol(sa::ptx::g_prof_cycles, z, 64 * 8);
+    cudaMemcpyToSymbol(sa::ptx::g_prof_count, z, 64 * 8);
+    return 0;
+}
+#endif
+
 const char* sa_strerror(int status) {
     switch (status) {
         case SA_OK: return "ok";

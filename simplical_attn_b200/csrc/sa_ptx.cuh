@@ -53,11 +53,32 @@ struct WaitCtx {
     DeviceStatus* status;        // global memory
 };
 
+#ifdef SA_PROFILE
+// Profiling builds only: cycles block 0 spent in each wait site (indexed by the site id) and how
+// often, read back through sa_prof_read.
+__device__ unsigned long long g_prof_cycles[64];
+__device__ unsigned long long g_prof_count[64];
+#endif
+
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait in these kernels
 
 // Waits for the phase with the given parity.  Bounded: after kWaitLimitNs it records where it gave
 // up, raises the block's abort flag and returns false.
+__device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where);
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where) {
+#ifdef SA_PROFILE
+    const long long t0 = clock64();
+    const bool r = mbar_wait_impl(bar, parity, ctx, where);
+    if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {
+        atomicAdd(&g_prof_cycles[where & 63], (unsigned long long)(clock64() - t0));
+        atomicAdd(&g_prof_count[where & 63], 1ull);
+    }
+    return r;
+#else
+    return mbar_wait_impl(bar, parity, ctx, where);
+#endif
+}
+__device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where) {
     if (mbar_try_wait(bar, parity)) return true;
     uint64_t t0 = 0;
     uint32_t spins = 0;

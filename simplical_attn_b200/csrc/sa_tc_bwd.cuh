@@ -521,6 +521,36 @@ __device__ __forceinline__ void load_bf16_cw(const __nv_bfloat16* row, int col, 
     }
 }
 
+
+// Index into a ring of fp32 rows [slot][HD]; the low five column bits are XOR-ed with the slot so
+// that a warp whose lanes hold the same column of 32 consecutive rows hits 32 different banks.
+template <int HD>
+__device__ __forceinline__ int ring_index(int slot, int col) {
+    return slot * HD + ((col & ~31) | ((col ^ slot) & 31));
+}
+
+// Sum over the 32 lanes of a warp of CW values per lane; afterwards lane L holds the total of
+// value (L % CW) in v[0].  A halving exchange: each step a lane keeps one half of its values and
+// adds the partner's copy of that half, 31 shuffles for 32 values.
+template <int CW>
+__device__ __forceinline__ float warp_transpose_reduce(float (&v)[CW], int lane) {
+    if constexpr (CW == 16) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] += __shfl_xor_sync(0xffffffffu, v[j], 16);
+    }
+#pragma unroll
+    for (int s = (CW == 32 ? 16 : 8); s >= 1; s >>= 1) {
+        const bool upper = (lane & s) != 0;
+#pragma unroll
+        for (int j = 0; j < s; ++j) {
+            const float send = upper ? v[j] : v[j + s];
+            const float keep = upper ? v[j + s] : v[j];
+            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+        }
+    }
+    return v[0];
+}
+
 template <int HD>
 __global__ void __launch_bounds__(kRowThreads, 1)
 bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
@@ -651,28 +681,71 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const int kb_max = min(i0 + qpt, p.N) - 1 + p.halo2;
                 const int own0 = ri.i_run0 + p.halo2;                        // first row owned by this run
                 if (uidx == 0) flush_lo = max(0, own0 - (p.w2 - 1));
-                // the factors of this thread's row, fetched one chunk ahead of their use
-                uint4 yraw[2][CW / 8], xraw[2][CW / 8];
-#pragma unroll
-                for (int x = 0; x < CW / 8; ++x) {
-                    yraw[0][x] = ((const uint4*)y_row)[x];
-                    if (grp == 0) xraw[0][x] = ((const uint4*)k2_row)[x];
-                }
                 mbar_wait(B.acc_ready, n_units & 1, wctx, 31);
                 tc_fence_after();
+                if (P.dw_log2 >= 5 && (ring_rows > 0 || !need_kv2)) {
+                    // ---- a warp holds 32 consecutive deltas of one query: its lanes own distinct K2 rows.
+                    // Warp w works on column chunk (w + phase) % 4, so no two warps touch the same ring
+                    // columns at the same time; the delta sum for dQ is a register exchange inside the warp.
+                    const int wq = row >> 5;
+                    float* dq_part = scr_a;                              // [4 warps][HD]
+                    const int slot = row_valid ? kb % max(ring_rows, 1) : 0;
+#pragma unroll 1
+                    for (int ph = 0; ph < 4; ++ph) {
+                        const int c = (wq + ph) & 3;
+                        uint4 yraw[CW / 8], xraw[CW / 8];
 #pragma unroll
+                        for (int x = 0; x < CW / 8; ++x) {
+                            yraw[x] = ((const uint4*)(y_row + c * CW))[x];
+                            if (grp == 0) xraw[x] = ((const uint4*)(k2_row + c * CW))[x];
+                        }
+                        uint32_t g[CW];
+                        tmem_ld_cw<CW>(acc + c * CW, g);
+                        const __nv_bfloat16* yh = (const __nv_bfloat16*)yraw;
+                        const __nv_bfloat16* xh = (const __nv_bfloat16*)xraw;
+                        if (grp == 0 && dq != nullptr) {
+                            float v[CW];
+#pragma unroll
+                            for (int e = 0; e < CW; ++e)
+                                v[e] = row_valid ? __uint_as_float(g[e]) * (__bfloat162float(xh[e]) + p.k2_bias) * mult : 0.f;
+                            const float tot = warp_transpose_reduce<CW>(v, lane);
+                            if (lane < CW) dq_part[wq * HD + c * CW + lane] = tot;
+                        }
+                        if (need_kv2 && row_valid) {
+#pragma unroll
+                            for (int e = 0; e < CW; ++e)
+                                ring[ring_index<HD>(slot, c * CW + e)] += __uint_as_float(g[e]) * __bfloat162float(yh[e]) * mult;
+                        }
+                        named_barrier_sync(1 + grp, 128);
+                    }
+                    if (grp == 0 && dq != nullptr) {
+                        // warps per query = DW / 32; thread t finishes column t of every query of the tile
+                        const int wpq = DW >> 5;
+                        if (row < HD) {
+                            for (int q2 = 0; q2 < qpt; ++q2) {
+                                float a = 0.f;
+                                for (int w2i = 0; w2i < wpq; ++w2i) a += dq_part[(q2 * wpq + w2i) * HD + row];
+                                if (i0 + q2 < p.N)
+                                    dq[ri.b * p.dq.b + (long)(i0 + q2) * p.dq.n + ri.h * p.dq.h + row] = __float2bfloat16_rn(a);
+                            }
+                        }
+                        named_barrier_sync(1 + grp, 128);
+                    }
+                } else {
+                // ---- general path (several queries per warp, or no room for the ring): stage the scaled
+                // rows in shared memory and sum them per output row
+#pragma unroll 1
                 for (int c = 0; c < HD / CW; ++c) {
                     uint32_t g[CW];
                     tmem_ld_cw<CW>(acc + c * CW, g);
-                    if (c + 1 < HD / CW) {
+                    uint4 yraw[CW / 8], xraw[CW / 8];
 #pragma unroll
-                        for (int x = 0; x < CW / 8; ++x) {
-                            yraw[(c + 1) & 1][x] = ((const uint4*)(y_row + (c + 1) * CW))[x];
-                            if (grp == 0) xraw[(c + 1) & 1][x] = ((const uint4*)(k2_row + (c + 1) * CW))[x];
-                        }
+                    for (int x = 0; x < CW / 8; ++x) {
+                        yraw[x] = ((const uint4*)(y_row + c * CW))[x];
+                        if (grp == 0) xraw[x] = ((const uint4*)(k2_row + c * CW))[x];
                     }
-                    const __nv_bfloat16* yh = (const __nv_bfloat16*)yraw[c & 1];
-                    const __nv_bfloat16* xh = (const __nv_bfloat16*)xraw[c & 1];
+                    const __nv_bfloat16* yh = (const __nv_bfloat16*)yraw;
+                    const __nv_bfloat16* xh = (const __nv_bfloat16*)xraw;
                     if (grp == 0) {
 #pragma unroll
                         for (int e = 0; e < CW; ++e)
@@ -711,7 +784,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                                 }
                             }
                             if (ring_rows > 0) {
-                                ring[(kbt % ring_rows) * HD + c * CW + e] += a;
+                                ring[ring_index<HD>(kbt % ring_rows, c * CW + e)] += a;
                             } else {
                                 // no room for the ring: accumulate in the workspace (this block alone touches the row)
                                 float* dst;
@@ -730,17 +803,19 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     }
                     named_barrier_sync(1 + grp, 128);
                 }
+                }
                 if (need_kv2 && ring_rows > 0) {
                     // rows no later query of the run reaches are final: move them to the workspace, clear the slots
                     const bool last_unit = i0 + qpt >= ri.i_run1;
                     const int f_hi = last_unit ? kb_max + 1 : max(0, i0 + qpt + p.halo2 - (p.w2 - 1));
                     for (int kbf = flush_lo; kbf < f_hi; ++kbf) {
-                        float* src = ring + (kbf % ring_rows) * HD;
+                        const int slot = kbf % ring_rows;
                         float* dst = (kbf >= own0) ? ws_full + (bh * p.N + (kbf - p.halo2)) * HD
                                                    : ws_head + ((bh * P.num_runs + ri.run) * (p.w2 - 1) + (kbf - (own0 - (p.w2 - 1)))) * HD;
                         for (int d = row; d < HD; d += 128) {
-                            dst[d] = src[d];
-                            src[d] = 0.f;
+                            float* src = ring + ring_index<HD>(slot, d);
+                            dst[d] = *src;
+                            *src = 0.f;
                         }
                     }
                     flush_lo = max(flush_lo, f_hi);
