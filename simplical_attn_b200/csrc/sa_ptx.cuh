@@ -60,6 +60,20 @@ __device__ unsigned long long g_prof_cycles[64];
 __device__ unsigned long long g_prof_count[64];
 #endif
 
+#ifdef SA_PROFILE
+#define SA_PROF_T0(name) const long long name = clock64()
+#define SA_PROF_ADD(site, t0)                                                              \
+    do {                                                                                   \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) {                                  \
+            atomicAdd(&sa::ptx::g_prof_cycles[(site) & 63], (unsigned long long)(clock64() - (t0))); \
+            atomicAdd(&sa::ptx::g_prof_count[(site) & 63], 1ull);                          \
+        }                                                                                  \
+    } while (0)
+#else
+#define SA_PROF_T0(name) do { } while (0)
+#define SA_PROF_ADD(site, t0) do { } while (0)
+#endif
+
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait in these kernels
 
 // Waits for the phase with the given parity.  Bounded: after kWaitLimitNs it records where it gave
@@ -100,6 +114,13 @@ __device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, c
         }
     }
 }
+
+// Per-warpgroup register re-allocation: the data-movement warps give registers up, the softmax /
+// epilogue warps take them.  N is a multiple of 8; all four warps of an aligned warpgroup execute it.
+template <int N>
+__device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 
 // Makes generic-proxy writes to shared memory visible to the async proxy (TMA, tcgen05.mma).
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -257,37 +278,43 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 
+// bf16 pair held in a 32-bit word -> floats, by bit operations only (a register array reinterpreted
+// through a pointer cast tends to be demoted to local memory).
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// Loads N consecutive bf16 values (N a multiple of 8, 16-byte aligned) as N/2 packed words.
+template <int N>
+__device__ __forceinline__ void load_bf16_words(const __nv_bfloat16* src, uint32_t (&w)[N / 2]) {
+#pragma unroll
+    for (int x = 0; x < N / 8; ++x) {
+        const uint4 t = ((const uint4*)src)[x];
+        w[4 * x] = t.x;
+        w[4 * x + 1] = t.y;
+        w[4 * x + 2] = t.z;
+        w[4 * x + 3] = t.w;
+    }
+}
+
 // Product of two bf16 chunks of 8 elements, x * (y + bias), computed in fp32 and rounded once.
 __device__ __forceinline__ uint4 mul_chunk(const uint4& xa, const uint4& ya, float bias) {
-    const __nv_bfloat162* xh = (const __nv_bfloat162*)&xa;
-    const __nv_bfloat162* yh = (const __nv_bfloat162*)&ya;
+    const uint32_t xw[4] = {xa.x, xa.y, xa.z, xa.w}, yw[4] = {ya.x, ya.y, ya.z, ya.w};
     uint32_t w[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-        const float2 xf = __bfloat1622float2(xh[e]);
-        const float2 yf = __bfloat1622float2(yh[e]);
-        w[e] = pack_bf16(xf.x * (yf.x + bias), xf.y * (yf.y + bias));
-    }
+    for (int e = 0; e < 4; ++e)
+        w[e] = pack_bf16(bf16_lo(xw[e]) * (bf16_lo(yw[e]) + bias), bf16_hi(xw[e]) * (bf16_hi(yw[e]) + bias));
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
-// Forms `nrows` rows of a 128-byte-swizzled operand tile ([nrows x 64] slabs, `slab_bytes` apart)
-// with `nthreads` cooperating threads (`t` = index of this thread among them).  Tile row r is the
-// virtual row rho = rho0 + r:  i = rho >> dw_log2,  delta = rho & (DW-1),  kb = i + halo2 - delta,
-//     row = x[i, :] * (y[kb, :] + bias)          (zeros when i >= n_q, delta >= w2 or kb < 0)
-// where x and y point at row 0 of the right batch and head and have row strides xs, ys (elements).
-// Consecutive threads take consecutive 16-byte chunks of a row, so global loads coalesce and the
-// shared-memory stores of a quarter warp hit eight distinct 16-byte slots of one 128-byte line.
 // With bias == 0 the product of two bf16 values rounded to bf16 is exactly what the packed bf16
 // multiply returns (the product of two 8-bit significands is exact in fp32, one rounding follows).
-__device__ __forceinline__ uint4 mul_chunk_nobias(const uint4& xa, const uint4& ya) {
-    uint4 r;
-    const __nv_bfloat162* xh = (const __nv_bfloat162*)&xa;
-    const __nv_bfloat162* yh = (const __nv_bfloat162*)&ya;
-    __nv_bfloat162* rh = (__nv_bfloat162*)&r;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) rh[e] = __hmul2(xh[e], yh[e]);
+__device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
+    uint32_t r;
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
+}
+__device__ __forceinline__ uint4 mul_chunk_nobias(const uint4& xa, const uint4& ya) {
+    return make_uint4(hmul2_bf16(xa.x, ya.x), hmul2_bf16(xa.y, ya.y), hmul2_bf16(xa.z, ya.z), hmul2_bf16(xa.w, ya.w));
 }
 
 template <int HD, int NROWS, int NTHREADS>

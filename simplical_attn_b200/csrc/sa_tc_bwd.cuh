@@ -37,7 +37,7 @@ namespace sa {
 namespace tc {
 
 constexpr int kBwdThreads = 512;      // column kernel: 2 softmax groups, producer group, MMA and TMA warps
-constexpr int kRowThreads = 320;      // row kernel: 2 softmax groups, MMA warp (8), TMA warp (9)
+constexpr int kRowThreads = 384;      // row kernel: 2 softmax groups, MMA warp (8), TMA warp (9), 2 idle warps
 constexpr int kStreamRows = 64;        // rows of a streamed tile = columns of an S / dP tile
 constexpr int kBwdStages = 3;          // streamed-tile ring depth
 
@@ -186,31 +186,45 @@ __device__ __forceinline__ BwdBars bwd_bars(uint64_t* b) {
 // [64 x HD] of which the first `width` rows count.
 //   S_b  = X W^T,   dP_b = Y Z^T              (issue_sdp)
 //   acc1 += P_b Z,  acc2 += dS_b W            (issue_acc; P_b, dS_b read from tensor memory)
+// The issuing thread is a single lane, so every integer instruction between two MMAs delays the
+// tensor pipe: descriptors are built once per tile from the tile's address and only advanced by
+// constants (a descriptor's low bits hold the address in 16-byte units, and no operand here ends
+// beyond 256 KiB, so adding to the 64-bit value never carries out of the address field).
 template <int HD>
 __device__ __forceinline__ void issue_sdp(uint32_t tm_s, uint32_t tm_dp, uint32_t x, uint32_t y, uint32_t w, uint32_t z,
-                                          int width) {
+                                          uint32_t idesc) {
     using L = BwdSmem<HD>;
-    const uint32_t idesc = ptx::make_idesc(128, width, false, false);
+    const uint64_t dx = ptx::desc_kmajor(x, 0), dy = ptx::desc_kmajor(y, 0);
+    const uint64_t dw = ptx::desc_kmajor(w, 0), dz = ptx::desc_kmajor(z, 0);
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk)
-        ptx::mma_ss(tm_s, ptx::desc_kmajor(x + (kk >> 2) * L::kBigSlab, kk & 3),
-                    ptx::desc_kmajor(w + (kk >> 2) * L::kSmallSlab, kk & 3), idesc, kk > 0);
+        ptx::mma_ss(tm_s, dx + (((kk >> 2) * L::kBigSlab + (kk & 3) * 32) >> 4),
+                    dw + (((kk >> 2) * L::kSmallSlab + (kk & 3) * 32) >> 4), idesc, kk > 0);
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk)
-        ptx::mma_ss(tm_dp, ptx::desc_kmajor(y + (kk >> 2) * L::kBigSlab, kk & 3),
-                    ptx::desc_kmajor(z + (kk >> 2) * L::kSmallSlab, kk & 3), idesc, kk > 0);
+        ptx::mma_ss(tm_dp, dy + (((kk >> 2) * L::kBigSlab + (kk & 3) * 32) >> 4),
+                    dz + (((kk >> 2) * L::kSmallSlab + (kk & 3) * 32) >> 4), idesc, kk > 0);
 }
 
 template <int HD>
 __device__ __forceinline__ void issue_acc(uint32_t tm_acc1, uint32_t tm_acc2, uint32_t tm_p, uint32_t tm_ds, uint32_t w,
-                                          uint32_t z, int width, bool accumulate) {
+                                          uint32_t z, int ksteps, bool accumulate) {
     using L = BwdSmem<HD>;
     const uint32_t idesc = ptx::make_idesc(128, HD, false, true);
-    const int ksteps = width / 16;
-    for (int kk = 0; kk < ksteps; ++kk)
-        ptx::mma_ts(tm_acc1, tm_p + kk * 8, ptx::desc_mnmajor(z + kk * 2048, L::kSmallSlab), idesc, accumulate || kk > 0);
-    for (int kk = 0; kk < ksteps; ++kk)
-        ptx::mma_ts(tm_acc2, tm_ds + kk * 8, ptx::desc_mnmajor(w + kk * 2048, L::kSmallSlab), idesc, accumulate || kk > 0);
+    const uint64_t dw = ptx::desc_mnmajor(w, L::kSmallSlab), dz = ptx::desc_mnmajor(z, L::kSmallSlab);
+    if (ksteps == kStreamRows / 16) {
+#pragma unroll
+        for (int kk = 0; kk < kStreamRows / 16; ++kk)
+            ptx::mma_ts(tm_acc1, tm_p + kk * 8, dz + kk * (2048 >> 4), idesc, accumulate || kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < kStreamRows / 16; ++kk)
+            ptx::mma_ts(tm_acc2, tm_ds + kk * 8, dw + kk * (2048 >> 4), idesc, accumulate || kk > 0);
+    } else {
+        for (int kk = 0; kk < ksteps; ++kk)
+            ptx::mma_ts(tm_acc1, tm_p + kk * 8, dz + kk * (2048 >> 4), idesc, accumulate || kk > 0);
+        for (int kk = 0; kk < ksteps; ++kk)
+            ptx::mma_ts(tm_acc2, tm_ds + kk * 8, dw + kk * (2048 >> 4), idesc, accumulate || kk > 0);
+    }
 }
 
 template <int HD>
@@ -389,6 +403,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             uint32_t nb[2] = {0, 0}, g_base = 0, n_items = 0;
+            const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false);
             const uint32_t k1s = smem_base + L::kStat0, v1s = smem_base + L::kStat1;
             for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
                 const ColItem ci = col_item(P, it);
@@ -404,7 +419,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         const uint32_t a_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, c_t = a_t + L::kSmallTile;
                         mbar_wait(&B.st_full[stage], (g / kBwdStages) & 1, wctx, 25);
                         tc_fence_after();
-                        issue_sdp<HD>(tm_s[b], tm_dp[b], k1s, v1s, a_t, c_t, kStreamRows);
+                        issue_sdp<HD>(tm_s[b], tm_dp[b], k1s, v1s, a_t, c_t, idesc_full);
                         tc_commit(&B.sdp_ready[b]);
                     }
                     if (t >= 1) {
@@ -416,7 +431,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         ++nb[b];
                         tc_fence_after();
                         // dV1 += P^T-tile * C-tile ; dK1 += dS^T-tile * A-tile
-                        issue_acc<HD>(tm_dv1, tm_dk1, tm_s[b], tm_dp[b], a_t, c_t, kStreamRows, tp > 0);
+                        issue_acc<HD>(tm_dv1, tm_dk1, tm_s[b], tm_dp[b], a_t, c_t, kStreamRows / 16, tp > 0);
                         tc_commit(&B.st_empty[stage]);
                     }
                 }
@@ -602,6 +617,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 
     if (warp < 8) {
         // ---------------------------------------------------------------- softmax groups + epilogue
+        reg_alloc<232>();
         const int grp = warp >> 2;
         const int row = tid & 127;
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
@@ -631,6 +647,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const __nv_bfloat16* k2_row = k2 + ri.b * p.k2.b + (long)kc * p.k2.n + ri.hk * p.k2.h;
                 const __nv_bfloat16* v2_row = v2 + ri.b * p.v2.b + (long)kc * p.v2.n + ri.hk * p.v2.h;
                 // ---- stationary operand of this group
+                SA_PROF_T0(t_form);
                 if (grp == 0)
                     form_product_tile<HD, 128, 128>(my_tile, L::kBigSlab, row, (long)i0 << P.dw_log2, P.dw_log2, p.N, p.w2, p.halo2,
                                           q + ri.b * p.q.b + ri.h * p.q.h, p.q.n, k2 + ri.b * p.k2.b + ri.hk * p.k2.h, p.k2.n,
@@ -642,6 +659,8 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 fence_proxy_async_smem();
                 tc_fence_before();
                 mbar_arrive(B.stat_full);
+                SA_PROF_ADD(40 + grp, t_form);
+                SA_PROF_T0(t_loop);
                 const long li = ((long)ri.b * p.H + ri.h) * p.N + ic;
                 const float lse2 = P.lse2[li], dlt_i = P.delta[li];
                 const int jhi = row_valid ? i + p.halo1 : -1;
@@ -681,8 +700,10 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const int kb_max = min(i0 + qpt, p.N) - 1 + p.halo2;
                 const int own0 = ri.i_run0 + p.halo2;                        // first row owned by this run
                 if (uidx == 0) flush_lo = max(0, own0 - (p.w2 - 1));
+                SA_PROF_ADD(42 + grp, t_loop);
                 mbar_wait(B.acc_ready, n_units & 1, wctx, 31);
                 tc_fence_after();
+                SA_PROF_T0(t_epi);
                 if (P.dw_log2 >= 5 && (ring_rows > 0 || !need_kv2)) {
                     // ---- a warp holds 32 consecutive deltas of one query: its lanes own distinct K2 rows.
                     // Warp w works on column chunk (w + phase) % 4, so no two warps touch the same ring
@@ -693,30 +714,43 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 #pragma unroll 1
                     for (int ph = 0; ph < 4; ++ph) {
                         const int c = (wq + ph) & 3;
-                        uint4 yraw[CW / 8], xraw[CW / 8];
-#pragma unroll
-                        for (int x = 0; x < CW / 8; ++x) {
-                            yraw[x] = ((const uint4*)(y_row + c * CW))[x];
-                            if (grp == 0) xraw[x] = ((const uint4*)(k2_row + c * CW))[x];
-                        }
+                        SA_PROF_T0(t_p0);
+                        uint32_t yw[CW / 2], xw[CW / 2];
+                        load_bf16_words<CW>(y_row + c * CW, yw);
+                        if (grp == 0) load_bf16_words<CW>(k2_row + c * CW, xw);
                         uint32_t g[CW];
                         tmem_ld_cw<CW>(acc + c * CW, g);
-                        const __nv_bfloat16* yh = (const __nv_bfloat16*)yraw;
-                        const __nv_bfloat16* xh = (const __nv_bfloat16*)xraw;
+                        SA_PROF_ADD(50 + 4 * grp, t_p0);
+                        SA_PROF_T0(t_p1);
                         if (grp == 0 && dq != nullptr) {
                             float v[CW];
 #pragma unroll
-                            for (int e = 0; e < CW; ++e)
-                                v[e] = row_valid ? __uint_as_float(g[e]) * (__bfloat162float(xh[e]) + p.k2_bias) * mult : 0.f;
+                            for (int e = 0; e < CW; e += 2) {
+                                v[e] = row_valid ? __uint_as_float(g[e]) * (bf16_lo(xw[e >> 1]) + p.k2_bias) * mult : 0.f;
+                                v[e + 1] = row_valid ? __uint_as_float(g[e + 1]) * (bf16_hi(xw[e >> 1]) + p.k2_bias) * mult : 0.f;
+                            }
                             const float tot = warp_transpose_reduce<CW>(v, lane);
                             if (lane < CW) dq_part[wq * HD + c * CW + lane] = tot;
                         }
+                        SA_PROF_ADD(51 + 4 * grp, t_p1);
+                        SA_PROF_T0(t_p2);
                         if (need_kv2 && row_valid) {
+                            // staged read-modify-write: all loads, then all adds, then all stores
+                            float acc_r[CW];
 #pragma unroll
-                            for (int e = 0; e < CW; ++e)
-                                ring[ring_index<HD>(slot, c * CW + e)] += __uint_as_float(g[e]) * __bfloat162float(yh[e]) * mult;
+                            for (int e = 0; e < CW; ++e) acc_r[e] = ring[ring_index<HD>(slot, c * CW + e)];
+#pragma unroll
+                            for (int e = 0; e < CW; e += 2) {
+                                acc_r[e] += __uint_as_float(g[e]) * bf16_lo(yw[e >> 1]) * mult;
+                                acc_r[e + 1] += __uint_as_float(g[e + 1]) * bf16_hi(yw[e >> 1]) * mult;
+                            }
+#pragma unroll
+                            for (int e = 0; e < CW; ++e) ring[ring_index<HD>(slot, c * CW + e)] = acc_r[e];
                         }
+                        SA_PROF_ADD(52 + 4 * grp, t_p2);
+                        SA_PROF_T0(t_p3);
                         named_barrier_sync(1 + grp, 128);
+                        SA_PROF_ADD(53 + 4 * grp, t_p3);
                     }
                     if (grp == 0 && dq != nullptr) {
                         // warps per query = DW / 32; thread t finishes column t of every query of the tile
@@ -738,24 +772,21 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 for (int c = 0; c < HD / CW; ++c) {
                     uint32_t g[CW];
                     tmem_ld_cw<CW>(acc + c * CW, g);
-                    uint4 yraw[CW / 8], xraw[CW / 8];
-#pragma unroll
-                    for (int x = 0; x < CW / 8; ++x) {
-                        yraw[x] = ((const uint4*)(y_row + c * CW))[x];
-                        if (grp == 0) xraw[x] = ((const uint4*)(k2_row + c * CW))[x];
-                    }
-                    const __nv_bfloat16* yh = (const __nv_bfloat16*)yraw;
-                    const __nv_bfloat16* xh = (const __nv_bfloat16*)xraw;
+                    uint32_t yw[CW / 2], xw[CW / 2];
+                    load_bf16_words<CW>(y_row + c * CW, yw);
                     if (grp == 0) {
+                        load_bf16_words<CW>(k2_row + c * CW, xw);
 #pragma unroll
-                        for (int e = 0; e < CW; ++e)
-                            scr_a[row * CW + (e ^ (row & (CW - 1)))] =
-                                row_valid ? __uint_as_float(g[e]) * (__bfloat162float(xh[e]) + p.k2_bias) * mult : 0.f;
+                        for (int e = 0; e < CW; ++e) {
+                            const float xf = ((e & 1) ? bf16_hi(xw[e >> 1]) : bf16_lo(xw[e >> 1])) + p.k2_bias;
+                            scr_a[row * CW + (e ^ (row & (CW - 1)))] = row_valid ? __uint_as_float(g[e]) * xf * mult : 0.f;
+                        }
                     }
 #pragma unroll
-                    for (int e = 0; e < CW; ++e)
-                        scr_b[row * CW + (e ^ (row & (CW - 1)))] =
-                            row_valid ? __uint_as_float(g[e]) * __bfloat162float(yh[e]) * mult : 0.f;
+                    for (int e = 0; e < CW; ++e) {
+                        const float yf = (e & 1) ? bf16_hi(yw[e >> 1]) : bf16_lo(yw[e >> 1]);
+                        scr_b[row * CW + (e ^ (row & (CW - 1)))] = row_valid ? __uint_as_float(g[e]) * yf * mult : 0.f;
+                    }
                     named_barrier_sync(1 + grp, 128);
                     if (grp == 0 && dq != nullptr) {
                         for (int idx = row; idx < qpt * CW; idx += 128) {
@@ -820,14 +851,17 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     }
                     flush_lo = max(flush_lo, f_hi);
                 }
+                SA_PROF_ADD(44 + grp, t_epi);
                 tc_fence_before();
                 mbar_arrive(B.acc_free);
             }
         }
     } else if (warp == 8) {
         // ---------------------------------------------------------------- MMA issuer
+        reg_dealloc<40>();
         if (lane == 0) {
             uint32_t nb[2] = {0, 0}, g_base = 0, n_units = 0;
+            const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false);
             const uint32_t a_s = smem_base + L::kStat0, c_s = smem_base + L::kStat1;
             for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
                 const RowItem ri = row_item(P, it);
@@ -835,6 +869,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     const RowUnit ru = row_unit(P, i0);
                     mbar_wait(B.stat_full, n_units & 1, wctx, 32);      // A, C formed (implies last epilogue done)
                     tc_fence_after();
+                    SA_PROF_T0(t_mma);
                     for (int t = 0; t <= ru.nt; ++t) {
                         if (t < ru.nt) {
                             const uint32_t g = g_base + t;
@@ -843,8 +878,10 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
                             mbar_wait(&B.st_full[stage], (g / kBwdStages) & 1, wctx, 33);
                             tc_fence_after();
-                            issue_sdp<HD>(tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width);
+                            SA_PROF_T0(t_i1);
+                            issue_sdp<HD>(tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false));
                             tc_commit(&B.sdp_ready[b]);
+                            SA_PROF_ADD(47, t_i1);
                         }
                         if (t >= 1) {
                             const int tp = t - 1;
@@ -856,11 +893,14 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             ++nb[b];
                             tc_fence_after();
                             // U += P V1-tile ; G += dS K1-tile
-                            issue_acc<HD>(tm_u, tm_g, tm_s[b], tm_dp[b], k1_t, v1_t, width, tp > 0);
+                            SA_PROF_T0(t_i2);
+                            issue_acc<HD>(tm_u, tm_g, tm_s[b], tm_dp[b], k1_t, v1_t, width / 16, tp > 0);
                             tc_commit(&B.st_empty[stage]);
+                            SA_PROF_ADD(48, t_i2);
                         }
                     }
                     tc_commit(B.acc_ready);
+                    SA_PROF_ADD(46, t_mma);
                     g_base += ru.nt;
                 }
             }
@@ -868,6 +908,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         __syncwarp();
     } else if (warp == 9) {
         // ---------------------------------------------------------------- TMA: streamed K1 / V1 tiles
+        reg_dealloc<40>();
         if (lane == 0) {
             prefetch_tensormap(&map_k1);
             prefetch_tensormap(&map_v1);
@@ -893,6 +934,8 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
             }
         }
         __syncwarp();
+    } else {
+        reg_dealloc<40>();
     }
     tc_fence_before();
     __syncthreads();

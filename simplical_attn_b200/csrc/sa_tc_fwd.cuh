@@ -177,6 +177,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc_pv = make_idesc(128, HD, false, true);
+            const uint32_t idesc_s_full = make_idesc(128, kColTile, false, false);
             uint32_t g = 0;          // ring position of the unit's first tile
             uint32_t nu = 0;         // units done (phase of a_ready / o_ready)
             uint32_t ns[2] = {0, 0}; // S tiles issued per row tile (phase of s_ready / p_ready)
@@ -185,24 +186,28 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                 auto width_of = [&](int t) { return t == ug.ntiles - 1 ? ug.last_width : kColTile; };
                 auto issue_s = [&](int r, int t) {
                     const int s = (g + t) % kStages;
-                    const uint32_t idesc_s = make_idesc(128, width_of(t), false, false);
-                    const uint32_t a_addr = smem_base + L::kA + r * L::kTileBytes;
-                    const uint32_t b_addr = smem_base + L::kK1 + s * L::kTileBytes;
+                    const uint32_t idesc_s = (t == ug.ntiles - 1) ? make_idesc(128, ug.last_width, false, false) : idesc_s_full;
+                    const uint64_t da = desc_kmajor(smem_base + L::kA + r * L::kTileBytes, 0);
+                    const uint64_t db = desc_kmajor(smem_base + L::kK1 + s * L::kTileBytes, 0);
 #pragma unroll
                     for (int kk = 0; kk < HD / 16; ++kk) {
-                        const uint32_t slab = (kk >> 2) * L::kSlabBytes;
-                        mma_ss(tmem_s[r], desc_kmajor(a_addr + slab, kk & 3), desc_kmajor(b_addr + slab, kk & 3), idesc_s,
-                               kk > 0);
+                        const uint32_t off = ((kk >> 2) * L::kSlabBytes + (kk & 3) * 32) >> 4;
+                        mma_ss(tmem_s[r], da + off, db + off, idesc_s, kk > 0);
                     }
                     tc_commit(&s_ready[r]);
                 };
                 auto issue_pv = [&](int r, int t) {
                     const int s = (g + t) % kStages;
-                    const uint32_t b_addr = smem_base + L::kV1 + s * L::kTileBytes;
-                    const int ksteps = width_of(t) / 16;
-                    for (int kk = 0; kk < ksteps; ++kk)
-                        mma_ts(tmem_t[r], tmem_s[r] + kk * 8, desc_mnmajor(b_addr + kk * 2048, L::kSlabBytes), idesc_pv,
-                               t > 0 || kk > 0);
+                    const uint64_t db = desc_mnmajor(smem_base + L::kV1 + s * L::kTileBytes, L::kSlabBytes);
+                    if (t != ug.ntiles - 1) {
+#pragma unroll
+                        for (int kk = 0; kk < kColTile / 16; ++kk)
+                            mma_ts(tmem_t[r], tmem_s[r] + kk * 8, db + kk * (2048 >> 4), idesc_pv, t > 0 || kk > 0);
+                    } else {
+                        const int ksteps = ug.last_width / 16;
+                        for (int kk = 0; kk < ksteps; ++kk)
+                            mma_ts(tmem_t[r], tmem_s[r] + kk * 8, db + kk * (2048 >> 4), idesc_pv, t > 0 || kk > 0);
+                    }
                 };
                 // prologue: S(0) of both row tiles
                 mbar_wait(&k1_full[g % kStages], (g / kStages) & 1, wctx, 3);
@@ -352,13 +357,14 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                 uint32_t v[32];
                 tmem_ld32(t_addr + c0, v);
                 tmem_wait_ld();
-                uint4 vv[4];
+                uint32_t vw[16];
 #pragma unroll
-                for (int e = 0; e < 4; ++e) vv[e] = row_valid ? ((const uint4*)(v2row + c0))[e] : make_uint4(0, 0, 0, 0);
-                const __nv_bfloat16* vh = (const __nv_bfloat16*)vv;
+                for (int e = 0; e < 16; ++e) vw[e] = 0u;
+                if (row_valid) load_bf16_words<32>(v2row + c0, vw);
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
-                    const float val = row_valid ? __uint_as_float(v[e]) * wrow * (__bfloat162float(vh[e]) + p.v2_bias) : 0.f;
+                    const float vf = (e & 1) ? bf16_hi(vw[e >> 1]) : bf16_lo(vw[e >> 1]);
+                    const float val = row_valid ? __uint_as_float(v[e]) * wrow * (vf + p.v2_bias) : 0.f;
                     scratch[row * 32 + (e ^ (row & 31))] = val;
                 }
                 named_barrier_sync(1 + r, kRowTile);
