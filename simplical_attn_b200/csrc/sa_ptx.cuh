@@ -317,7 +317,7 @@ __device__ __forceinline__ uint4 mul_chunk_nobias(const uint4& xa, const uint4& 
     return make_uint4(hmul2_bf16(xa.x, ya.x), hmul2_bf16(xa.y, ya.y), hmul2_bf16(xa.z, ya.z), hmul2_bf16(xa.w, ya.w));
 }
 
-template <int HD, int NROWS, int NTHREADS>
+template <int HD, int NROWS, int NTHREADS, int MAXBATCH = 4>
 __device__ __forceinline__ void form_product_tile(uint8_t* tile, int slab_bytes, int t, long rho0, int dw_log2, int n_q,
                                                   int w2, int halo2, const __nv_bfloat16* x, int64_t xs,
                                                   const __nv_bfloat16* y, int64_t ys, float bias) {
@@ -325,7 +325,7 @@ __device__ __forceinline__ void form_product_tile(uint8_t* tile, int slab_bytes,
     constexpr int RPP = NTHREADS / C;            // rows per pass
     constexpr int PASSES = NROWS / RPP;
     static_assert(NROWS % RPP == 0, "tile rows must be a multiple of the rows formed per pass");
-    constexpr int BATCH = PASSES < 4 ? PASSES : 4;    // loads in flight per thread: 2 * BATCH 16-byte loads
+    constexpr int BATCH = PASSES < MAXBATCH ? PASSES : MAXBATCH;    // loads in flight per thread: 2 * BATCH 16-byte loads
     static_assert(PASSES % BATCH == 0, "passes must split into whole batches");
     const int c = t % C;
     const int dmask = (1 << dw_log2) - 1;

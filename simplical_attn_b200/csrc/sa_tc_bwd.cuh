@@ -39,7 +39,8 @@ namespace tc {
 constexpr int kBwdThreads = 512;      // column kernel: 2 softmax groups, producer group, MMA and TMA warps
 constexpr int kRowThreads = 384;      // row kernel: 2 softmax groups, MMA warp (8), TMA warp (9), 2 idle warps
 constexpr int kStreamRows = 64;        // rows of a streamed tile = columns of an S / dP tile
-constexpr int kBwdStages = 3;          // streamed-tile ring depth
+constexpr int kColStages = 4;          // streamed-tile ring depth of the column kernel
+constexpr int kRowStages = 3;          // ... of the row kernel (its dK2/dV2 ring needs the room)
 
 struct BwdTcParams {
     KParams k;
@@ -60,7 +61,7 @@ struct BwdTcParams {
     DeviceStatus* status;
 };
 
-template <int HD>
+template <int HD, int NS = kRowStages>
 struct BwdSmem {
     static constexpr int kSlabs = HD / 64;
     static constexpr int kBigTile = 128 * HD * 2;            // stationary tile  [128 x HD]
@@ -69,10 +70,10 @@ struct BwdSmem {
     static constexpr int kSmallSlab = kStreamRows * 128;
     static constexpr int kStat0 = 0;                         // K1 (column kernel) / A (row kernel)
     static constexpr int kStat1 = kBigTile;                  // V1 / C
-    static constexpr int kStream = 2 * kBigTile;             // kBwdStages x (tile0 | tile1)
-    static constexpr int kMeta = kStream + kBwdStages * 2 * kSmallTile;   // per stage: 64 lse2 + 64 delta
-    static constexpr int kBars = kMeta + kBwdStages * 128 * 4;
-    static constexpr int kNumBars = 2 * kBwdStages + 10;
+    static constexpr int kStream = 2 * kBigTile;             // NS x (tile0 | tile1)
+    static constexpr int kMeta = kStream + NS * 2 * kSmallTile;   // per stage: 64 lse2 + 64 delta
+    static constexpr int kBars = kMeta + NS * 128 * 4;
+    static constexpr int kNumBars = 2 * NS + 10;
     static constexpr int kMisc = kBars + kNumBars * 8;
     static constexpr int kTotal = kMisc + 16;
     static constexpr int kRing = kTotal;                     // row kernel: 2 x ring_rows x HD floats (optional)
@@ -167,8 +168,8 @@ __device__ __forceinline__ ColItem col_item(const BwdTcParams& P, long it) {
 
 // Barrier block shared by the two big kernels.
 struct BwdBars {
-    uint64_t* st_full;     // [kBwdStages] streamed tile ready
-    uint64_t* st_empty;    // [kBwdStages] streamed tile consumed (tcgen05.commit)
+    uint64_t* st_full;     // [stages] streamed tile ready
+    uint64_t* st_empty;    // [stages] streamed tile consumed (tcgen05.commit)
     uint64_t* sdp_ready;   // [2] S and dP of buffer b computed (commit)
     uint64_t* pds_ready;   // [2] P and dS of buffer b stored (128 arrivals)
     uint64_t* stat_full;   // stationary tiles ready
@@ -177,9 +178,9 @@ struct BwdBars {
     uint64_t* acc_free;    // accumulators read out (256 arrivals)
 };
 
+template <int NS>
 __device__ __forceinline__ BwdBars bwd_bars(uint64_t* b) {
-    return BwdBars{b, b + kBwdStages, b + 2 * kBwdStages, b + 2 * kBwdStages + 2, b + 2 * kBwdStages + 4,
-                   b + 2 * kBwdStages + 5, b + 2 * kBwdStages + 6, b + 2 * kBwdStages + 7};
+    return BwdBars{b, b + NS, b + 2 * NS, b + 2 * NS + 2, b + 2 * NS + 4, b + 2 * NS + 5, b + 2 * NS + 6, b + 2 * NS + 7};
 }
 
 // The MMAs of one streamed tile.  `X`, `Y`: stationary tiles [128 x HD]; `W`, `Z`: streamed tiles
@@ -233,20 +234,20 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
                const __nv_bfloat16* __restrict__ k2, const __nv_bfloat16* __restrict__ v2,
                const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dk1, __nv_bfloat16* __restrict__ dv1) {
-    using L = BwdSmem<HD>;
+    using L = BwdSmem<HD, kColStages>;
     using namespace ptx;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
     const KParams& p = P.k;
-    const BwdBars B = bwd_bars((uint64_t*)(smem + L::kBars));
+    const BwdBars B = bwd_bars<kColStages>((uint64_t*)(smem + L::kBars));
     uint32_t* tmem_slot = (uint32_t*)(smem + L::kMisc);
     volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
     const WaitCtx wctx{abort_flag, P.status};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < kBwdStages; ++s) {
+        for (int s = 0; s < kColStages; ++s) {
             mbar_init(&B.st_full[s], 128);
             mbar_init(&B.st_empty[s], 1);
         }
@@ -276,6 +277,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 
     if (warp < 8) {
         // ---------------------------------------------------------------- softmax groups + epilogue
+        reg_alloc<144>();
         const int grp = warp >> 2;
         const int row = tid & 127;                       // tensor-memory lane = K1/V1 row of the tile
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
@@ -286,7 +288,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
             const int jb = ci.j0 + row;
             const int nt = ci.ntq * p.G;
             for (int t = grp; t < nt; t += 2, ++n_mine) {
-                const int stage = (int)((g_base + t) % kBwdStages);
+                const int stage = (int)((g_base + t) % kColStages);
                 const float* m_lse = (const float*)(smem + L::kMeta) + stage * 128;
                 const float* m_delta = m_lse + 64;
                 const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kStreamRows;
@@ -366,6 +368,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         }
     } else if (warp < 12) {
         // ---------------------------------------------------------------- producer of the A / C tiles
+        reg_alloc<152>();
         const int ptid = tid - 256;
         uint32_t g_base = 0;
         for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
@@ -373,17 +376,20 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
             const int nt = ci.ntq * p.G;
             for (int t = 0; t < nt; ++t) {
                 const uint32_t g = g_base + t;
-                const int stage = (int)(g % kBwdStages);
+                const int stage = (int)(g % kColStages);
                 const int h = ci.hk * p.G + t / ci.ntq;
                 const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kStreamRows;
-                mbar_wait(&B.st_empty[stage], ((g / kBwdStages) & 1) ^ 1, wctx, 22);
                 uint8_t* a_tile = smem + L::kStream + stage * 2 * L::kSmallTile;
-                form_product_tile<HD, kStreamRows, 128>(a_tile, L::kSmallSlab, ptid, rho0, P.dw_log2, p.N, p.w2, p.halo2,
-                                      q + ci.b * p.q.b + h * p.q.h, p.q.n, k2 + ci.b * p.k2.b + ci.hk * p.k2.h, p.k2.n,
-                                      p.k2_bias);
-                form_product_tile<HD, kStreamRows, 128>(a_tile + L::kSmallTile, L::kSmallSlab, ptid, rho0, P.dw_log2, p.N, p.w2,
-                                      p.halo2, d_o + ci.b * p.d_o.b + h * p.d_o.h, p.d_o.n,
-                                      v2 + ci.b * p.v2.b + ci.hk * p.v2.h, p.v2.n, p.v2_bias);
+                uint8_t* c_tile = a_tile + L::kSmallTile;
+                {
+                    mbar_wait(&B.st_empty[stage], ((g / kColStages) & 1) ^ 1, wctx, 22);
+                    form_product_tile<HD, kStreamRows, 128>(a_tile, L::kSmallSlab, ptid, rho0, P.dw_log2, p.N, p.w2, p.halo2,
+                                                            q + ci.b * p.q.b + h * p.q.h, p.q.n,
+                                                            k2 + ci.b * p.k2.b + ci.hk * p.k2.h, p.k2.n, p.k2_bias);
+                    form_product_tile<HD, kStreamRows, 128>(c_tile, L::kSmallSlab, ptid, rho0, P.dw_log2, p.N, p.w2, p.halo2,
+                                                            d_o + ci.b * p.d_o.b + h * p.d_o.h, p.d_o.n,
+                                                            v2 + ci.b * p.v2.b + ci.hk * p.v2.h, p.v2.n, p.v2_bias);
+                }
                 // LSE2 and Delta of the tile's queries
                 const int iq0 = (int)(rho0 >> P.dw_log2);
                 const int nq = max(1, kStreamRows >> P.dw_log2);
@@ -401,6 +407,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         }
     } else if (warp == 12) {
         // ---------------------------------------------------------------- MMA issuer
+        reg_dealloc<72>();
         if (lane == 0) {
             uint32_t nb[2] = {0, 0}, g_base = 0, n_items = 0;
             const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false);
@@ -415,9 +422,9 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 for (int t = 0; t <= nt; ++t) {
                     if (t < nt) {
                         const uint32_t g = g_base + t;
-                        const int stage = (int)(g % kBwdStages), b = t & 1;
+                        const int stage = (int)(g % kColStages), b = t & 1;
                         const uint32_t a_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, c_t = a_t + L::kSmallTile;
-                        mbar_wait(&B.st_full[stage], (g / kBwdStages) & 1, wctx, 25);
+                        mbar_wait(&B.st_full[stage], (g / kColStages) & 1, wctx, 25);
                         tc_fence_after();
                         issue_sdp<HD>(tm_s[b], tm_dp[b], k1s, v1s, a_t, c_t, idesc_full);
                         tc_commit(&B.sdp_ready[b]);
@@ -425,7 +432,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     if (t >= 1) {
                         const int tp = t - 1;
                         const uint32_t g = g_base + tp;
-                        const int stage = (int)(g % kBwdStages), b = tp & 1;
+                        const int stage = (int)(g % kColStages), b = tp & 1;
                         const uint32_t a_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, c_t = a_t + L::kSmallTile;
                         mbar_wait(&B.pds_ready[b], nb[b] & 1, wctx, 26);
                         ++nb[b];
@@ -444,6 +451,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         __syncwarp();
     } else if (warp == 13) {
         // ---------------------------------------------------------------- TMA: the block's K1 / V1 rows
+        reg_dealloc<72>();
         if (lane == 0) {
             prefetch_tensormap(&map_k1);
             prefetch_tensormap(&map_v1);
@@ -462,6 +470,8 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
             }
         }
         __syncwarp();
+    } else {
+        reg_dealloc<72>();
     }
     tc_fence_before();
     __syncthreads();
@@ -572,21 +582,21 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
                const __nv_bfloat16* __restrict__ k2, const __nv_bfloat16* __restrict__ v2,
                const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dq, int need_kv2, int ring_rows) {
-    using L = BwdSmem<HD>;
+    using L = BwdSmem<HD, kRowStages>;
     using namespace ptx;
     constexpr int CW = HD / 4;                            // epilogue chunk width
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
     const KParams& p = P.k;
-    const BwdBars B = bwd_bars((uint64_t*)(smem + L::kBars));
+    const BwdBars B = bwd_bars<kRowStages>((uint64_t*)(smem + L::kBars));
     uint32_t* tmem_slot = (uint32_t*)(smem + L::kMisc);
     volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
     const WaitCtx wctx{abort_flag, P.status};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < kBwdStages; ++s) {
+        for (int s = 0; s < kRowStages; ++s) {
             mbar_init(&B.st_full[s], 1);
             mbar_init(&B.st_empty[s], 1);
         }
@@ -617,7 +627,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 
     if (warp < 8) {
         // ---------------------------------------------------------------- softmax groups + epilogue
-        reg_alloc<232>();
+        reg_alloc<216>();
         const int grp = warp >> 2;
         const int row = tid & 127;
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
@@ -858,7 +868,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         }
     } else if (warp == 8) {
         // ---------------------------------------------------------------- MMA issuer
-        reg_dealloc<40>();
+        reg_dealloc<72>();
         if (lane == 0) {
             uint32_t nb[2] = {0, 0}, g_base = 0, n_units = 0;
             const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false);
@@ -873,10 +883,10 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     for (int t = 0; t <= ru.nt; ++t) {
                         if (t < ru.nt) {
                             const uint32_t g = g_base + t;
-                            const int stage = (int)(g % kBwdStages), b = t & 1;
+                            const int stage = (int)(g % kRowStages), b = t & 1;
                             const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
                             const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
-                            mbar_wait(&B.st_full[stage], (g / kBwdStages) & 1, wctx, 33);
+                            mbar_wait(&B.st_full[stage], (g / kRowStages) & 1, wctx, 33);
                             tc_fence_after();
                             SA_PROF_T0(t_i1);
                             issue_sdp<HD>(tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false));
@@ -886,7 +896,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         if (t >= 1) {
                             const int tp = t - 1;
                             const uint32_t g = g_base + tp;
-                            const int stage = (int)(g % kBwdStages), b = tp & 1;
+                            const int stage = (int)(g % kRowStages), b = tp & 1;
                             const int width = (tp == ru.nt - 1) ? ru.last_width : kStreamRows;
                             const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
                             mbar_wait(&B.pds_ready[b], nb[b] & 1, wctx, 34);
@@ -908,7 +918,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         __syncwarp();
     } else if (warp == 9) {
         // ---------------------------------------------------------------- TMA: streamed K1 / V1 tiles
-        reg_dealloc<40>();
+        reg_dealloc<72>();
         if (lane == 0) {
             prefetch_tensormap(&map_k1);
             prefetch_tensormap(&map_v1);
@@ -918,11 +928,11 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 for (int i0 = ri.i_run0; i0 < ri.i_run1; i0 += qpt) {
                     const RowUnit ru = row_unit(P, i0);
                     for (int t = 0; t < ru.nt; ++t, ++g) {
-                        const int stage = (int)(g % kBwdStages);
+                        const int stage = (int)(g % kRowStages);
                         const int r0 = ru.col_start + t * kStreamRows;
                         uint8_t* k1_t = smem + L::kStream + stage * 2 * L::kSmallTile;
                         uint8_t* v1_t = k1_t + L::kSmallTile;
-                        mbar_wait(&B.st_empty[stage], ((g / kBwdStages) & 1) ^ 1, wctx, 35);
+                        mbar_wait(&B.st_empty[stage], ((g / kRowStages) & 1) ^ 1, wctx, 35);
                         mbar_arrive_expect_tx(&B.st_full[stage], 2 * L::kSmallTile);
 #pragma unroll
                         for (int sl = 0; sl < L::kSlabs; ++sl) {
@@ -935,7 +945,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         }
         __syncwarp();
     } else {
-        reg_dealloc<40>();
+        reg_dealloc<72>();
     }
     tc_fence_before();
     __syncthreads();
@@ -1059,15 +1069,17 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         const long grid = P.num_col_items < sm_count ? P.num_col_items : sm_count;
         if (k.D == 128) {
             auto kern = bwd_col_kernel<128>;
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<128>::kAlloc) != cudaSuccess)
+            using LC = BwdSmem<128, kColStages>;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LC::kAlloc) != cudaSuccess)
                 return SA_ERR_LAUNCH;
-            kern<<<(unsigned)grid, kBwdThreads, BwdSmem<128>::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
+            kern<<<(unsigned)grid, kBwdThreads, LC::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
                                                                              (__nv_bfloat16*)dk1, (__nv_bfloat16*)dv1);
         } else {
             auto kern = bwd_col_kernel<64>;
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdSmem<64>::kAlloc) != cudaSuccess)
+            using LC = BwdSmem<64, kColStages>;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LC::kAlloc) != cudaSuccess)
                 return SA_ERR_LAUNCH;
-            kern<<<(unsigned)grid, kBwdThreads, BwdSmem<64>::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
+            kern<<<(unsigned)grid, kBwdThreads, LC::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
                                                                             (__nv_bfloat16*)dk1, (__nv_bfloat16*)dv1);
         }
         ++*nlaunch;
@@ -1081,7 +1093,7 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         // shared-memory ring of fp32 dK2/dV2 rows if it fits beside the tiles
         int ring_rows = (1 << pl.dw_log2) + pl.qpt;
         if (k.D == 128) {
-            using L = BwdSmem<128>;
+            using L = BwdSmem<128, kRowStages>;
             int smem = L::kTotal + 1024 + 2 * ring_rows * 128 * 4;
             if (!need_kv2 || smem > L::kMaxDynamic) { ring_rows = 0; smem = L::kAlloc; }
             if (smem < L::kAlloc) smem = L::kAlloc;
@@ -1091,7 +1103,7 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
             kern<<<(unsigned)grid, kRowThreads, smem, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o), (__nv_bfloat16*)dq,
                                                             need_kv2, ring_rows);
         } else {
-            using L = BwdSmem<64>;
+            using L = BwdSmem<64, kRowStages>;
             int smem = L::kTotal + 1024 + 2 * ring_rows * 64 * 4;
             if (!need_kv2 || smem > L::kMaxDynamic) { ring_rows = 0; smem = L::kAlloc; }
             if (smem < L::kAlloc) smem = L::kAlloc;
