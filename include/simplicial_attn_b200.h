@@ -79,6 +79,23 @@ int sa_backward(const sa_params* p, const void* q, const void* k1, const void* k
                 const void* v2, const void* o, const float* lse, const void* d_o, void* dq, void* dk1,
                 void* dk2, void* dv1, void* dv2, void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same backward for callers that cannot allocate device memory -- code running inside a stream
+ * capture or a graph replay, inside a framework's allocator callback, or in a process whose memory
+ * pool is owned and fully handed out by someone else, where a cudaMalloc would fail, deadlock or
+ * break the capture.  It has no counterpart in the reference.  Instead of a caller workspace it uses
+ * a 32 MiB scratch array built into the library image (so every GPU that loads the library gives
+ * up that much memory until the process exits) and calls no cudaMalloc, cudaFree or other
+ * allocating routine.  Problems whose sa_backward_workspace_size() exceeds
+ * sa_backward_static_capacity() are rejected with SA_ERR_WORKSPACE.  The first call on each device
+ * looks the array's device address up (with that device current); make that call before any stream
+ * capture begins.  All calls on a device share the one array: two calls whose kernels may overlap
+ * on the GPU (different streams, no ordering between them) race on it, so keep them ordered.  The
+ * device status word is cleared at the start of every call. */
+int sa_backward_static(const sa_params* p, const void* q, const void* k1, const void* k2, const void* v1,
+                       const void* v2, const void* o, const float* lse, const void* d_o, void* dq, void* dk1,
+                       void* dk2, void* dv1, void* dv2, void* stream);
+size_t sa_backward_static_capacity(void);
+
 /* Workspace sizes in bytes for the given problem (the reference allocates its work buffers inside
  * the autograd function, triton_impl.py:23-25,73-77; here the caller does).  Never 0: the first
  * 256 bytes hold the device status word. */

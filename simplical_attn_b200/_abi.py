@@ -16,7 +16,8 @@ SA_BF16, SA_F16, SA_F32 = 0, 1, 2
 SA_ALGO_AUTO, SA_ALGO_GENERAL, SA_ALGO_TCGEN05 = 0, 1, 2
 
 EXPORTS = ("sa_forward", "sa_backward", "sa_forward_workspace_size", "sa_backward_workspace_size", "sa_read_status",
-           "sa_resolve_algo", "sa_strerror", "sa_version", "sa_kernel_launches")
+           "sa_resolve_algo", "sa_strerror", "sa_version", "sa_kernel_launches", "sa_backward_static",
+           "sa_backward_static_capacity")
 
 
 class Strides(ctypes.Structure):
@@ -57,6 +58,9 @@ def load():
     lib.sa_forward.restype = ctypes.c_int
     lib.sa_backward.argtypes = [pp] + [vp] * 14 + [sz, vp]
     lib.sa_backward.restype = ctypes.c_int
+    lib.sa_backward_static.argtypes = [pp] + [vp] * 14
+    lib.sa_backward_static.restype = ctypes.c_int
+    lib.sa_backward_static_capacity.restype = sz
     lib.sa_forward_workspace_size.argtypes = [pp]
     lib.sa_forward_workspace_size.restype = sz
     lib.sa_backward_workspace_size.argtypes = [pp]

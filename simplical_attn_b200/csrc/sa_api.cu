@@ -20,6 +20,12 @@ constexpr size_t kStatusBytes = 256;
 
 std::atomic<uint64_t> g_launches{0};      // kernels launched by this library in this process
 
+// Scratch of sa_backward_static: lives in the module image, so every GPU that loads the library
+// carries these bytes until the process exits.  In host code the symbol is only a handle; the
+// device address is looked up once per device (static_scratch below).
+constexpr size_t kStaticScratchBytes = 32u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 bool stride_ok8(const sa_strides& s) { return s.b % 8 == 0 && s.n % 8 == 0 && s.h % 8 == 0; }
 
@@ -120,6 +126,22 @@ DeviceInfo& device_info() {
         cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
     }
     return d;
+}
+
+// Device address of g_static_scratch on the current device, resolved on first use per device.
+void* static_scratch() {
+    static void* addr[64] = {nullptr};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    void*& slot = addr[dev & 63];
+    if (slot == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess) return nullptr;
+        slot = p;
+    }
+    return slot;
 }
 
 template <typename Kern>
@@ -288,6 +310,22 @@ int sa_backward(const sa_params* p, const void* q, const void* k1, const void* k
     const cudaError_t e = sa::general::launch_bwd(p->dtype, k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2, st);
     g_launches += (dq ? 1 : 0) + ((dk1 || dv1) ? 1 : 0) + ((dk2 || dv2) ? 1 : 0);
     return e == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
+}
+
+size_t sa_backward_static_capacity(void) { return kStaticScratchBytes; }
+
+int sa_backward_static(const sa_params* p, const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
+                       const void* o, const float* lse, const void* d_o, void* dq, void* dk1, void* dk2, void* dv1,
+                       void* dv2, void* stream) {
+    const int v = validate(p);
+    if (v != SA_OK) return v;
+    const size_t need = sa_backward_workspace_size(p);
+    if (need > kStaticScratchBytes) return SA_ERR_WORKSPACE;      // the built-in scratch is fixed-size
+    void* scratch = static_scratch();                             // first call per device resolves the address
+    if (!scratch) return SA_ERR_LAUNCH;
+    // the scratch keeps what the previous call left: the status word must start at zero
+    if (cudaMemsetAsync(scratch, 0, kStatusBytes, static_cast<cudaStream_t>(stream)) != cudaSuccess) return SA_ERR_LAUNCH;
+    return sa_backward(p, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2, scratch, kStaticScratchBytes, stream);
 }
 
 }  // extern "C"
