@@ -279,9 +279,15 @@ def main():
     clocks = sampler.stop() if sampler else None
 
     o, lse = sab.two_simplicial_attn_fwd_kernel(q, k1, k2, v1, v2, w1, w2, scale)
-    ms_fwd = time_phase(lambda: sab.two_simplicial_attn_fwd_kernel(q, k1, k2, v1, v2, w1, w2, scale), max(2, args.steps))
-    ms_bwd = time_phase(lambda: sab.two_simplicial_attn_bwd(q, k1, k2, v1, v2, o, lse, do, w1, w2, scale),
-                        max(2, args.steps))
+    reps = max(2, args.steps)
+    ms_fwd = time_phase(lambda: sab.two_simplicial_attn_fwd_kernel(q, k1, k2, v1, v2, w1, w2, scale), reps)
+    ms_bwd = time_phase(lambda: sab.two_simplicial_attn_bwd(q, k1, k2, v1, v2, o, lse, do, w1, w2, scale), reps)
+    # the two big backward kernels on their own (each call also runs the tiny Delta/LSE2 pre-pass,
+    # the second one the dK2/dV2 reduction: together < 1 % of the time)
+    ms_col = time_phase(lambda: sab.two_simplicial_attn_bwd(q, k1, k2, v1, v2, o, lse, do, w1, w2, scale,
+                                                            need=(False, True, False, True, False)), reps)
+    ms_row = time_phase(lambda: sab.two_simplicial_attn_bwd(q, k1, k2, v1, v2, o, lse, do, w1, w2, scale,
+                                                            need=(True, False, True, False, True)), reps)
     del o, lse
 
     ms_e2e = None
@@ -303,15 +309,24 @@ def main():
             setattr(p, nm, _abi.Strides(t.stride(0), t.stride(1), t.stride(2)))
         algo = _abi.load().sa_resolve_algo(ctypes.byref(p))
         family = {1: "general (CUDA cores)", 2: "tcgen05"}.get(algo, str(algo))
-        # dominant phase: whichever of forward (2 units) / backward (6 units) takes longer
-        if ms_bwd >= ms_fwd:
-            dom, dom_ms, dom_fl = "backward", ms_bwd, 6.0 * unit_rank
-        else:
-            dom, dom_ms, dom_fl = "forward", ms_fwd, 2.0 * unit_rank
+        # Per-kernel roofline.  Credited FLOPs (minimum contraction count, 8 units per step): forward 2
+        # (S, P.V1); column kernel 3 (dV1, dK1 and half of the shared S/dP recomputation); row kernel 3
+        # (G, U and the other half).  DRAM traffic per launch comes from the ncu capture of a one-batch
+        # case (profiles/), scaled by the rank's batch: traffic grows in proportion to the batch.
+        kernels = {
+            "fwd_tc_kernel": (ms_fwd, 2.0 * unit_rank, 198.8e6 * Bl),
+            "bwd_col_kernel": (ms_col, 3.0 * unit_rank, 249.0e6 * Bl),
+            "bwd_row_kernel": (ms_row, 3.0 * unit_rank, 396.2e6 * Bl),
+        }
+        dom = max(kernels, key=lambda k: kernels[k][0])
+        dom_ms, dom_fl, dom_traffic = kernels[dom]
         achieved = dom_fl / (dom_ms * 1e-3) / 1e12
         roof = {"bound": "tensor", "kernel": f"{dom} ({family})", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "peak_source": f"{peak_kind} bf16 sustained", "traffic": None,
+                "frac": achieved / peak, "peak_source": f"{peak_kind} bf16 sustained (cuBLAS)",
+                "traffic": dom_traffic if algo == 2 else None, "traffic_unit": "bytes per launch (ncu, scaled from batch 1)",
                 "frac_of_nominal_2250": achieved / 2250.0,
+                "per_kernel": {k: {"ms": v[0], "tflops": v[1] / (v[0] * 1e-3) / 1e12, "frac": v[1] / (v[0] * 1e-3) / 1e12 / peak}
+                               for k, v in kernels.items()},
                 "forward": {"ms": ms_fwd, "tflops": 2.0 * unit_rank / (ms_fwd * 1e-3) / 1e12},
                 "backward": {"ms": ms_bwd, "tflops": 6.0 * unit_rank / (ms_bwd * 1e-3) / 1e12}}
         line = {

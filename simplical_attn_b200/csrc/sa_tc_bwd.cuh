@@ -554,28 +554,6 @@ __device__ __forceinline__ int ring_index(int slot, int col) {
     return slot * HD + ((col & ~31) | ((col ^ slot) & 31));
 }
 
-// Sum over the 32 lanes of a warp of CW values per lane; afterwards lane L holds the total of
-// value (L % CW) in v[0].  A halving exchange: each step a lane keeps one half of its values and
-// adds the partner's copy of that half, 31 shuffles for 32 values.
-template <int CW>
-__device__ __forceinline__ float warp_transpose_reduce(float (&v)[CW], int lane) {
-    if constexpr (CW == 16) {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] += __shfl_xor_sync(0xffffffffu, v[j], 16);
-    }
-#pragma unroll
-    for (int s = (CW == 32 ? 16 : 8); s >= 1; s >>= 1) {
-        const bool upper = (lane & s) != 0;
-#pragma unroll
-        for (int j = 0; j < s; ++j) {
-            const float send = upper ? v[j] : v[j + s];
-            const float keep = upper ? v[j + s] : v[j];
-            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, s);
-        }
-    }
-    return v[0];
-}
-
 template <int HD>
 __global__ void __launch_bounds__(kRowThreads, 1)
 bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,

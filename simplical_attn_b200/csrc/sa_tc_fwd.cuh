@@ -29,7 +29,7 @@ constexpr int kRowTile = 128;          // virtual rows per row tile = tensor-mem
 constexpr int kColTile = 128;          // K1/V1 rows per column tile
 constexpr int kNumRowTiles = 2;        // row tiles per unit
 constexpr int kStages = 2;             // K1/V1 ring depth
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 384;       // 2 softmax groups, TMA warp (8), MMA warp (9), 2 idle warps
 constexpr float kRescaleThreshold = 8.0f;   // log2 units; below it the running maximum is kept
 
 struct FwdTcParams {
@@ -147,6 +147,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
 
     if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer
+        reg_dealloc<72>();
         if (lane == 0) {
             prefetch_tensormap(&map_k1);
             prefetch_tensormap(&map_v1);
@@ -175,6 +176,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
         __syncwarp();
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
+        reg_dealloc<72>();
         if (lane == 0) {
             const uint32_t idesc_pv = make_idesc(128, HD, false, true);
             const uint32_t idesc_s_full = make_idesc(128, kColTile, false, false);
@@ -242,8 +244,11 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
             }
         }
         __syncwarp();
+    } else if (warp >= 10) {
+        reg_dealloc<72>();
     } else {
         // ------------------------------------------------------------------ softmax / epilogue groups
+        reg_alloc<216>();
         const int r = warp >> 2;                     // row tile of this group
         const int row = tid & 127;                   // virtual row = tensor-memory lane
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;   // lane base of this warp
@@ -261,11 +266,14 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
             const int kb = i + p.halo2 - delta;                    // K2/V2 buffer row
             const bool row_valid = (i < p.N) && (delta < p.w2) && (kb >= 0);
             // ---- form A_r: row (i, delta) = Q_i * (K2_{i-delta} + bias) as bf16, 128-byte swizzled
+            SA_PROF_T0(t_form);
             form_product_tile<HD, kRowTile, kRowTile>(a_tile, L::kSlabBytes, row, (long)(ug.i0 + r * qpt) << P.dw_log2, P.dw_log2,
                                   p.N, p.w2, p.halo2, q + ug.b * p.q.b + ug.h * p.q.h, p.q.n,
                                   k2 + ug.b * p.k2.b + ug.hk * p.k2.h, p.k2.n, p.k2_bias);
             fence_proxy_async_smem();
             mbar_arrive(&a_ready[r]);
+            SA_PROF_ADD(10 + r, t_form);
+            SA_PROF_T0(t_loop);
             // ---- main loop over column tiles
             // Valid buffer rows of this virtual row: [jlo, jhi] (empty for an invalid row).
             const int jhi = row_valid ? i + p.halo1 : -1;
@@ -277,67 +285,104 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                 const int lo = jlo - tile0, hi = jhi - tile0;        // valid tile-relative columns [lo, hi]
                 mbar_wait(&s_ready[r], ns & 1, wctx, 8);
                 tc_fence_after();
+                SA_PROF_T0(t_sm);
                 const uint32_t s_addr = tmem_s[r] + lane_addr;
-                // pass 1: row maximum of the valid columns
-                float tmax = -INFINITY;
-                for (int c0 = 0; c0 < width; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(s_addr + c0, v);
+                // a tile is "full" when every column is inside every row's window: no masks needed
+                const bool full = (width == kColTile) && __all_sync(0xffffffffu, lo <= 0 && hi >= kColTile - 1);
+                float lsum = 0.f;
+                // running maximum, lazily updated: returns the factor the row's T and l must be scaled by
+                auto update_max = [&](float tmax) {
+                    float factor = 1.f;
+                    bool rescale = false;
+                    if (tmax > m + kRescaleThreshold || (m == -INFINITY && tmax > -INFINITY)) {
+                        rescale = (m != -INFINITY);
+                        factor = rescale ? ex2(m - tmax) : 1.f;
+                        m = tmax;
+                    }
+                    if (__any_sync(0xffffffffu, rescale)) {
+                        l *= factor;
+                        const uint32_t t_addr = tmem_t[r] + lane_addr;
+#pragma unroll
+                        for (int c0 = 0; c0 < HD; c0 += 32) {
+                            uint32_t tv[32];
+                            tmem_ld32(t_addr + c0, tv);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) tv[e] = __float_as_uint(__uint_as_float(tv[e]) * factor);
+                            tmem_st32(t_addr + c0, tv);
+                        }
+                    }
+                };
+                if (full) {
+                    // single pass: the whole row of S sits in registers
+                    uint32_t v[4][32];
+#pragma unroll
+                    for (int cch = 0; cch < 4; ++cch) tmem_ld32(s_addr + 32 * cch, v[cch]);
                     tmem_wait_ld();
+                    float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
-                        const int c = c0 + e;
-                        if (c >= lo && c <= hi) tmax = fmaxf(tmax, __uint_as_float(v[e]));
-                    }
-                }
-                tmax *= c2;                                            // -inf stays -inf (c2 > 0)
-                // running maximum, lazily updated
-                float factor = 1.f;
-                bool rescale = false;
-                if (tmax > m + kRescaleThreshold || (m == -INFINITY && tmax > -INFINITY)) {
-                    rescale = (m != -INFINITY);
-                    factor = rescale ? ex2(m - tmax) : 1.f;
-                    m = tmax;
-                }
-                if (__any_sync(0xffffffffu, rescale)) {
-                    l *= factor;
-                    const uint32_t t_addr = tmem_t[r] + lane_addr;
 #pragma unroll
-                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        for (int cch = 0; cch < 4; ++cch) mx[cch] = fmaxf(mx[cch], __uint_as_float(v[cch][e]));
+                    }
+                    update_max(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c2);
+                    float ls[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int cch = 0; cch < 4; ++cch) {
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int e = 0; e < 32; e += 2) {
+                            const float p0 = ex2(fmaf(__uint_as_float(v[cch][e]), c2, -m));
+                            const float p1 = ex2(fmaf(__uint_as_float(v[cch][e + 1]), c2, -m));
+                            ls[cch] += p0 + p1;
+                            pk[e >> 1] = pack_bf16(p0, p1);
+                        }
+                        tmem_st16(s_addr + 16 * cch, pk);
+                    }
+                    lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                } else {
+                    // pass 1: row maximum of the valid columns
+                    float tmax = -INFINITY;
+                    for (int c0 = 0; c0 < width; c0 += 32) {
                         uint32_t v[32];
-                        tmem_ld32(t_addr + c0, v);
+                        tmem_ld32(s_addr + c0, v);
                         tmem_wait_ld();
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
-                        tmem_st32(t_addr + c0, v);
+                        for (int e = 0; e < 32; ++e) {
+                            const int c = c0 + e;
+                            if (c >= lo && c <= hi) tmax = fmaxf(tmax, __uint_as_float(v[e]));
+                        }
                     }
-                }
-                // pass 2: P = exp2(S*c2 - m), packed bf16 over the S columns already consumed
-                const float msafe = (m == -INFINITY) ? 0.f : m;
-                float lsum = 0.f;
-                for (int c0 = 0; c0 < width; c0 += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(s_addr + c0, v);
-                    tmem_wait_ld();
-                    uint32_t pk[16];
+                    update_max(tmax * c2);                                 // -inf stays -inf (c2 > 0)
+                    // pass 2: P = exp2(S*c2 - m), packed bf16 over the S columns already consumed
+                    const float msafe = (m == -INFINITY) ? 0.f : m;
+                    for (int c0 = 0; c0 < width; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld32(s_addr + c0, v);
+                        tmem_wait_ld();
+                        uint32_t pk[16];
 #pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
-                        const int c = c0 + e;
-                        float p0 = ex2(fmaf(__uint_as_float(v[e]), c2, -msafe));
-                        float p1 = ex2(fmaf(__uint_as_float(v[e + 1]), c2, -msafe));
-                        p0 = (c >= lo && c <= hi) ? p0 : 0.f;
-                        p1 = (c + 1 >= lo && c + 1 <= hi) ? p1 : 0.f;
-                        lsum += p0 + p1;
-                        pk[e >> 1] = pack_bf16(p0, p1);
+                        for (int e = 0; e < 32; e += 2) {
+                            const int c = c0 + e;
+                            float p0 = ex2(fmaf(__uint_as_float(v[e]), c2, -msafe));
+                            float p1 = ex2(fmaf(__uint_as_float(v[e + 1]), c2, -msafe));
+                            p0 = (c >= lo && c <= hi) ? p0 : 0.f;
+                            p1 = (c + 1 >= lo && c + 1 <= hi) ? p1 : 0.f;
+                            lsum += p0 + p1;
+                            pk[e >> 1] = pack_bf16(p0, p1);
+                        }
+                        tmem_st16(s_addr + (c0 >> 1), pk);
                     }
-                    tmem_st16(s_addr + (c0 >> 1), pk);
                 }
                 l += lsum;
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&p_ready[r]);
+                SA_PROF_ADD(16 + r, t_sm);
             }
             // ---- epilogue: merge the delta rows of each query
+            SA_PROF_ADD(12 + r, t_loop);
+            SA_PROF_T0(t_epi);
             m_s[row] = m;
             l_s[row] = l;
             named_barrier_sync(1 + r, kRowTile);
@@ -353,6 +398,50 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
             tc_fence_after();
             const __nv_bfloat16* v2row = v2 + ug.b * p.v2.b + (long)max(kb, 0) * p.v2.n + ug.hk * p.v2.h;
             const uint32_t t_addr = tmem_t[r] + lane_addr;
+            if (P.dw_log2 >= 5) {
+                // a warp holds 32 consecutive deltas of one query: sum them by a register exchange;
+                // lane L ends up with column L of each 32-column chunk
+                const int wq = row >> 5;                      // warp within the group
+                const int wpq = DW >> 5;                      // warps per query
+                float* part = scratch;                        // [4 warps][HD] when a query spans several warps
+                float tot[HD / 32];
+#pragma unroll
+                for (int cch = 0; cch < HD / 32; ++cch) {
+                    uint32_t v[32];
+                    tmem_ld32(t_addr + 32 * cch, v);
+                    uint32_t vw[16];
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) vw[e] = 0u;
+                    if (row_valid) load_bf16_words<32>(v2row + 32 * cch, vw);
+                    tmem_wait_ld();
+                    float y[32];
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) {
+                        y[e] = row_valid ? __uint_as_float(v[e]) * wrow * (bf16_lo(vw[e >> 1]) + p.v2_bias) : 0.f;
+                        y[e + 1] = row_valid ? __uint_as_float(v[e + 1]) * wrow * (bf16_hi(vw[e >> 1]) + p.v2_bias) : 0.f;
+                    }
+                    tot[cch] = warp_transpose_reduce<32>(y, lane);
+                }
+                if (wpq == 1) {
+                    if (i < p.N) {
+                        __nv_bfloat16* orow = o + ug.b * p.o.b + (long)i * p.o.n + ug.h * p.o.h;
+#pragma unroll
+                        for (int cch = 0; cch < HD / 32; ++cch) orow[32 * cch + lane] = __float2bfloat16_rn(tot[cch]);
+                    }
+                } else {
+#pragma unroll
+                    for (int cch = 0; cch < HD / 32; ++cch) part[wq * HD + 32 * cch + lane] = tot[cch];
+                    named_barrier_sync(1 + r, kRowTile);
+                    for (int idx = row; idx < qpt * HD; idx += kRowTile) {
+                        const int q2 = idx / HD, col = idx % HD;
+                        float acc = 0.f;
+                        for (int w2i = 0; w2i < wpq; ++w2i) acc += part[(q2 * wpq + w2i) * HD + col];
+                        const int i2 = ug.i0 + r * qpt + q2;
+                        if (i2 < p.N) o[ug.b * p.o.b + (long)i2 * p.o.n + ug.h * p.o.h + col] = __float2bfloat16_rn(acc);
+                    }
+                    named_barrier_sync(1 + r, kRowTile);
+                }
+            } else {
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(t_addr + c0, v);
@@ -380,7 +469,9 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                 }
                 named_barrier_sync(1 + r, kRowTile);
             }
+            }
             if (delta == 0 && i < p.N) lse[((long)ug.b * p.H + ug.h) * p.N + i] = (mq + log2f(lq)) * kLn2;
+            SA_PROF_ADD(14 + r, t_epi);
             tc_fence_before();
         }
     }
