@@ -340,9 +340,9 @@ __device__ __forceinline__ void form_product_tile(uint8_t* tile, int slab_bytes,
             const int dlt = (int)(rho & dmask);
             const int kb = i + halo2 - dlt;
             ok[k] = i < n_q && dlt < w2 && kb >= 0;
-            if (ok[k]) {
-                xa[k] = ((const uint4*)(x + (int64_t)i * xs))[c];
-                ya[k] = ((const uint4*)(y + (int64_t)kb * ys))[c];
+            if (ok[k]) {                          // read-only path: the rows are re-read by neighbouring tiles
+                xa[k] = __ldg((const uint4*)(x + (int64_t)i * xs) + c);
+                ya[k] = __ldg((const uint4*)(y + (int64_t)kb * ys) + c);
             }
         }
 #pragma unroll

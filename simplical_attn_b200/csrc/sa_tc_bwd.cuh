@@ -27,8 +27,8 @@
 // Both big kernels share one pipeline: S and dP tiles (128 lanes x 64 columns) are double buffered
 // in tensor memory; softmax group b (4 warps) turns buffer b into P and dS (bf16, in place) while the
 // tensor cores work on the other buffer; P and dS then feed the two accumulating MMAs from tensor
-// memory.  Warps 0-3 / 4-7: softmax groups, 8-11: tile producer (column kernel only), 12: MMA
-// issuer, 13: TMA issuer.
+// memory.  Warps 0-3 / 4-7: softmax groups (in the column kernel they also form the streamed A / C
+// tiles, four tiles ahead of their use), warp 8: MMA issuer, warp 9: TMA issuer.
 #pragma once
 
 #include "sa_ptx.cuh"
@@ -36,7 +36,7 @@
 namespace sa {
 namespace tc {
 
-constexpr int kBwdThreads = 512;      // column kernel: 2 softmax groups, producer group, MMA and TMA warps
+constexpr int kColThreads = 384;      // column kernel: 2 softmax/producer groups, MMA warp (8), TMA warp (9), 2 idle warps
 constexpr int kRowThreads = 384;      // row kernel: 2 softmax groups, MMA warp (8), TMA warp (9), 2 idle warps
 constexpr int kStreamRows = 64;        // rows of a streamed tile = columns of an S / dP tile
 constexpr int kColStages = 4;          // streamed-tile ring depth of the column kernel
@@ -229,7 +229,7 @@ __device__ __forceinline__ void issue_acc(uint32_t tm_acc1, uint32_t tm_acc2, ui
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kColThreads, 1)
 bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
                const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
                const __nv_bfloat16* __restrict__ k2, const __nv_bfloat16* __restrict__ v2,
@@ -262,7 +262,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 12) {
+    if (warp == 8) {
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
@@ -277,7 +277,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 
     if (warp < 8) {
         // ---------------------------------------------------------------- softmax groups + epilogue
-        reg_alloc<144>();
+        reg_alloc<216>();
         const int grp = warp >> 2;
         const int row = tid & 127;                       // tensor-memory lane = K1/V1 row of the tile
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
@@ -287,6 +287,34 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
             const ColItem ci = col_item(P, it);
             const int jb = ci.j0 + row;
             const int nt = ci.ntq * p.G;
+            // Each group also forms the A / C tiles of the streamed tiles it will process (its own, two of
+            // them ahead): A = Q * (K2 + bias), C = dO * (V2 + bias) for 64 virtual rows, from global memory.
+            auto form_tile = [&](int t) {
+                const uint32_t g = g_base + t;
+                const int stage = (int)(g % kColStages);
+                const int h = ci.hk * p.G + t / ci.ntq;
+                const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kStreamRows;
+                uint8_t* a_tile = smem + L::kStream + stage * 2 * L::kSmallTile;
+                mbar_wait(&B.st_empty[stage], ((g / kColStages) & 1) ^ 1, wctx, 22);
+                form_product_tile<HD, kStreamRows, 128>(a_tile, L::kSmallSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2,
+                                                           q + ci.b * p.q.b + h * p.q.h, p.q.n,
+                                                           k2 + ci.b * p.k2.b + ci.hk * p.k2.h, p.k2.n, p.k2_bias);
+                form_product_tile<HD, kStreamRows, 128>(a_tile + L::kSmallTile, L::kSmallSlab, row, rho0, P.dw_log2, p.N,
+                                                           p.w2, p.halo2, d_o + ci.b * p.d_o.b + h * p.d_o.h, p.d_o.n,
+                                                           v2 + ci.b * p.v2.b + ci.hk * p.v2.h, p.v2.n, p.v2_bias);
+                const int iq0 = (int)(rho0 >> P.dw_log2);
+                const int nq = max(1, kStreamRows >> P.dw_log2);
+                if (row < nq) {                              // LSE2 and Delta of the tile's queries
+                    const int i = iq0 + row;
+                    float* m_lse = (float*)(smem + L::kMeta) + stage * 128;
+                    const long li = ((long)ci.b * p.H + h) * p.N + min(i, p.N - 1);
+                    m_lse[row] = (i < p.N) ? P.lse2[li] : INFINITY;
+                    m_lse[64 + row] = (i < p.N) ? P.delta[li] : 0.f;
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(&B.st_full[stage]);
+            };
+            for (int t = grp; t < nt && t < grp + kColStages; t += 2) form_tile(t);
             for (int t = grp; t < nt; t += 2, ++n_mine) {
                 const int stage = (int)((g_base + t) % kColStages);
                 const float* m_lse = (const float*)(smem + L::kMeta) + stage * 128;
@@ -329,6 +357,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&B.pds_ready[grp]);
+                if (t + kColStages < nt) form_tile(t + kColStages);     // into the stage this tile is about to free
             }
             g_base += nt;
             // epilogue: group 0 writes dV1, group 1 writes dK1 (times scale)
@@ -366,46 +395,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 mbar_arrive(B.acc_free);
             }
         }
-    } else if (warp < 12) {
-        // ---------------------------------------------------------------- producer of the A / C tiles
-        reg_alloc<152>();
-        const int ptid = tid - 256;
-        uint32_t g_base = 0;
-        for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
-            const ColItem ci = col_item(P, it);
-            const int nt = ci.ntq * p.G;
-            for (int t = 0; t < nt; ++t) {
-                const uint32_t g = g_base + t;
-                const int stage = (int)(g % kColStages);
-                const int h = ci.hk * p.G + t / ci.ntq;
-                const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kStreamRows;
-                uint8_t* a_tile = smem + L::kStream + stage * 2 * L::kSmallTile;
-                uint8_t* c_tile = a_tile + L::kSmallTile;
-                {
-                    mbar_wait(&B.st_empty[stage], ((g / kColStages) & 1) ^ 1, wctx, 22);
-                    form_product_tile<HD, kStreamRows, 128>(a_tile, L::kSmallSlab, ptid, rho0, P.dw_log2, p.N, p.w2, p.halo2,
-                                                            q + ci.b * p.q.b + h * p.q.h, p.q.n,
-                                                            k2 + ci.b * p.k2.b + ci.hk * p.k2.h, p.k2.n, p.k2_bias);
-                    form_product_tile<HD, kStreamRows, 128>(c_tile, L::kSmallSlab, ptid, rho0, P.dw_log2, p.N, p.w2, p.halo2,
-                                                            d_o + ci.b * p.d_o.b + h * p.d_o.h, p.d_o.n,
-                                                            v2 + ci.b * p.v2.b + ci.hk * p.v2.h, p.v2.n, p.v2_bias);
-                }
-                // LSE2 and Delta of the tile's queries
-                const int iq0 = (int)(rho0 >> P.dw_log2);
-                const int nq = max(1, kStreamRows >> P.dw_log2);
-                if (ptid < nq) {
-                    const int i = iq0 + ptid;
-                    float* m_lse = (float*)(smem + L::kMeta) + stage * 128;
-                    const long li = ((long)ci.b * p.H + h) * p.N + min(i, p.N - 1);
-                    m_lse[ptid] = (i < p.N) ? P.lse2[li] : INFINITY;
-                    m_lse[64 + ptid] = (i < p.N) ? P.delta[li] : 0.f;
-                }
-                fence_proxy_async_smem();
-                mbar_arrive(&B.st_full[stage]);
-            }
-            g_base += nt;
-        }
-    } else if (warp == 12) {
+    } else if (warp == 8) {
         // ---------------------------------------------------------------- MMA issuer
         reg_dealloc<72>();
         if (lane == 0) {
@@ -449,7 +439,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
             }
         }
         __syncwarp();
-    } else if (warp == 13) {
+    } else if (warp == 9) {
         // ---------------------------------------------------------------- TMA: the block's K1 / V1 rows
         reg_dealloc<72>();
         if (lane == 0) {
@@ -475,7 +465,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 12) {
+    if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
@@ -1050,14 +1040,14 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
             using LC = BwdSmem<128, kColStages>;
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LC::kAlloc) != cudaSuccess)
                 return SA_ERR_LAUNCH;
-            kern<<<(unsigned)grid, kBwdThreads, LC::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
+            kern<<<(unsigned)grid, kColThreads, LC::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
                                                                              (__nv_bfloat16*)dk1, (__nv_bfloat16*)dv1);
         } else {
             auto kern = bwd_col_kernel<64>;
             using LC = BwdSmem<64, kColStages>;
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LC::kAlloc) != cudaSuccess)
                 return SA_ERR_LAUNCH;
-            kern<<<(unsigned)grid, kBwdThreads, LC::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
+            kern<<<(unsigned)grid, kColThreads, LC::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
                                                                             (__nv_bfloat16*)dk1, (__nv_bfloat16*)dv1);
         }
         ++*nlaunch;
