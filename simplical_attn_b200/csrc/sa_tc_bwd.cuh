@@ -36,10 +36,11 @@
 namespace sa {
 namespace tc {
 
-constexpr int kColThreads = 384;      // column kernel: 2 softmax/producer groups, MMA warp (8), TMA warp (9), 2 idle warps
+constexpr int kColThreads = 640;      // column kernel: 2 softmax groups, 2 producer groups, MMA warp (16), TMA warp (17), 2 idle
 constexpr int kRowThreads = 384;      // row kernel: 2 softmax groups, MMA warp (8), TMA warp (9), 2 idle warps
 constexpr int kStreamRows = 64;        // rows of a streamed tile = columns of an S / dP tile
-constexpr int kColStages = 4;          // streamed-tile ring depth of the column kernel
+constexpr int kColTileRows = 128;      // column kernel: virtual rows per streamed tile (columns of S^T)
+constexpr int kColStages = 2;          // ... and its ring depth
 constexpr int kRowStages = 3;          // ... of the row kernel (its dK2/dV2 ring needs the room)
 
 struct BwdTcParams {
@@ -109,13 +110,13 @@ prep_kernel(KParams p, const __nv_bfloat16* __restrict__ o, const __nv_bfloat16*
     }
 }
 
-// P = mask ? exp2(s*c2 - lse2) : 0 and dS = P * (dp - delta) for 32 columns, packed to bf16.
+// P = mask ? exp2(s*c2 - lse2) : 0 and dS = P * (dp - delta) for W columns, packed to bf16.
 // MASKED selects per-column validity through lo/hi (tile-relative valid column range).
-template <bool MASKED>
-__device__ __forceinline__ void softmax_bwd_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], int c0, int lo, int hi,
-                                                  float c2, float lse2, float delta, uint32_t (&pp)[16], uint32_t (&ds)[16]) {
+template <bool MASKED, int W = 32>
+__device__ __forceinline__ void softmax_bwd_chunk(const uint32_t (&s)[W], const uint32_t (&dp)[W], int c0, int lo, int hi,
+                                                  float c2, float lse2, float delta, uint32_t (&pp)[W / 2], uint32_t (&ds)[W / 2]) {
 #pragma unroll
-    for (int e = 0; e < 32; e += 2) {
+    for (int e = 0; e < W; e += 2) {
         float p0 = ptx::ex2(fmaf(__uint_as_float(s[e]), c2, -lse2));
         float p1 = ptx::ex2(fmaf(__uint_as_float(s[e + 1]), c2, -lse2));
         if (MASKED) {
@@ -140,7 +141,7 @@ __device__ __forceinline__ void softmax_bwd_chunk(const uint32_t (&s)[32], const
 // ------------------------------------------------------------------------------------------------
 struct ColItem {
     int b, hk, j0;        // first K1/V1 buffer row of the block's 128-row tile
-    int tt_lo, ntq;       // first streamed tile (64 virtual rows each) and tiles per query head
+    int tt_lo, ntq;       // first streamed tile (128 virtual rows each) and tiles per query head
 };
 
 __device__ __forceinline__ ColItem col_item(const BwdTcParams& P, long it) {
@@ -159,8 +160,8 @@ __device__ __forceinline__ ColItem col_item(const BwdTcParams& P, long it) {
         c.ntq = 0;
     } else {
         const long r_lo = (long)i_lo << P.dw_log2, r_hi = ((long)(i_hi + 1) << P.dw_log2);   // [r_lo, r_hi)
-        c.tt_lo = (int)(r_lo / kStreamRows);
-        c.ntq = (int)((r_hi + kStreamRows - 1) / kStreamRows) - c.tt_lo;
+        c.tt_lo = (int)(r_lo / kColTileRows);
+        c.ntq = (int)((r_hi + kColTileRows - 1) / kColTileRows) - c.tt_lo;
     }
     return c;
 }
@@ -228,19 +229,50 @@ __device__ __forceinline__ void issue_acc(uint32_t tm_acc1, uint32_t tm_acc2, ui
     }
 }
 
+// Shared-memory plan of the column kernel: the block's K1 and V1 rows, then kColStages pairs of
+// streamed tiles (A | C, 128 virtual rows each), per-stage LSE2 / Delta of the tile's queries.
+template <int HD>
+struct ColSmem {
+    static constexpr int kSlabs = HD / 64;
+    static constexpr int kTile = 128 * HD * 2;
+    static constexpr int kSlab = 128 * 128;
+    static constexpr int kK1 = 0;
+    static constexpr int kV1 = kTile;
+    static constexpr int kStream = 2 * kTile;
+    static constexpr int kMeta = kStream + kColStages * 2 * kTile;
+    static constexpr int kBars = kMeta + kColStages * 256 * 4;
+    static constexpr int kNumBars = 2 * kColStages + 6;
+    static constexpr int kMisc = kBars + kNumBars * 8;
+    static constexpr int kTotal = kMisc + 16;
+    static constexpr int kAlloc = (kTotal + 1024 > 120 * 1024) ? kTotal + 1024 : 120 * 1024;
+};
+
+// One streamed tile covers 128 virtual rows, so S^T and dP^T are single 128x128 tiles: the MMAs run
+// with N = 128 (a 128x64 tile costs almost as much: the 128-row stationary operand is re-read from
+// shared memory either way) and in long bursts.  S^T / dP^T are not double buffered (tensor memory
+// is full: 128 + 128 + 2 x 128 accumulator columns); instead both softmax groups work on the same
+// tile, group g on columns [64g, 64g + 64), and write P / dS back inside their own column range.
 template <int HD>
 __global__ void __launch_bounds__(kColThreads, 1)
 bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
                const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
                const __nv_bfloat16* __restrict__ k2, const __nv_bfloat16* __restrict__ v2,
                const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dk1, __nv_bfloat16* __restrict__ dv1) {
-    using L = BwdSmem<HD, kColStages>;
+    using L = ColSmem<HD>;
     using namespace ptx;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
     const KParams& p = P.k;
-    const BwdBars B = bwd_bars<kColStages>((uint64_t*)(smem + L::kBars));
+    uint64_t* bars = (uint64_t*)(smem + L::kBars);
+    uint64_t* st_full = bars;                         // [kColStages] A and C of a tile formed (256 arrivals)
+    uint64_t* st_empty = bars + kColStages;           // [kColStages] tile consumed (commit)
+    uint64_t* sdp_ready = bars + 2 * kColStages;      // S^T, dP^T computed (commit)
+    uint64_t* pds_ready = sdp_ready + 1;              // P^T, dS^T stored (256 arrivals)
+    uint64_t* stat_full = sdp_ready + 2;              // K1, V1 landed (TMA)
+    uint64_t* stat_empty = sdp_ready + 3;             // K1, V1 no longer read (commit)
+    uint64_t* acc_ready = sdp_ready + 4;              // dV1, dK1 final (commit)
+    uint64_t* acc_free = sdp_ready + 5;               // dV1, dK1 read out (256 arrivals)
     uint32_t* tmem_slot = (uint32_t*)(smem + L::kMisc);
     volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
     const WaitCtx wctx{abort_flag, P.status};
@@ -248,21 +280,19 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
         for (int s = 0; s < kColStages; ++s) {
-            mbar_init(&B.st_full[s], 128);
-            mbar_init(&B.st_empty[s], 1);
+            mbar_init(&st_full[s], 256);
+            mbar_init(&st_empty[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
-            mbar_init(&B.sdp_ready[b], 1);
-            mbar_init(&B.pds_ready[b], 128);
-        }
-        mbar_init(B.stat_full, 1);
-        mbar_init(B.stat_empty, 1);
-        mbar_init(B.acc_ready, 1);
-        mbar_init(B.acc_free, 256);
+        mbar_init(sdp_ready, 1);
+        mbar_init(pds_ready, 256);
+        mbar_init(stat_full, 1);
+        mbar_init(stat_empty, 1);
+        mbar_init(acc_ready, 1);
+        mbar_init(acc_free, 256);
         *abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 8) {
+    if (warp == 16) {
         tmem_alloc(tmem_slot, 512);
         tmem_relinquish();
     }
@@ -270,74 +300,45 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tm_s[2] = {tmem_base, tmem_base + 64};
-    const uint32_t tm_dp[2] = {tmem_base + 128, tmem_base + 192};
-    const uint32_t tm_dv1 = tmem_base + 256, tm_dk1 = tmem_base + 384;
-    const int DW = 1 << P.dw_log2;
+    const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dv1 = tmem_base + 256, tm_dk1 = tmem_base + 384;
 
     if (warp < 8) {
         // ---------------------------------------------------------------- softmax groups + epilogue
-        reg_alloc<216>();
+        reg_alloc<104>();      // 2 x 104 + 2 x 96 (producers) + 80 = 5 x 96: an increase beyond the block's own pool would never return
         const int grp = warp >> 2;
-        const int row = tid & 127;                       // tensor-memory lane = K1/V1 row of the tile
+        const int row = tid & 127;                       // tensor-memory lane = K1/V1 row of the block's tile
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
         const float c2 = p.scale * kLog2e;
-        uint32_t n_mine = 0, n_items = 0, g_base = 0;
+        uint32_t n_items = 0, g_base = 0;
         for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
             const ColItem ci = col_item(P, it);
             const int jb = ci.j0 + row;
             const int nt = ci.ntq * p.G;
-            // Each group also forms the A / C tiles of the streamed tiles it will process (its own, two of
-            // them ahead): A = Q * (K2 + bias), C = dO * (V2 + bias) for 64 virtual rows, from global memory.
-            auto form_tile = [&](int t) {
+            for (int t = 0; t < nt; ++t) {
                 const uint32_t g = g_base + t;
                 const int stage = (int)(g % kColStages);
-                const int h = ci.hk * p.G + t / ci.ntq;
-                const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kStreamRows;
-                uint8_t* a_tile = smem + L::kStream + stage * 2 * L::kSmallTile;
-                mbar_wait(&B.st_empty[stage], ((g / kColStages) & 1) ^ 1, wctx, 22);
-                form_product_tile<HD, kStreamRows, 128>(a_tile, L::kSmallSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2,
-                                                           q + ci.b * p.q.b + h * p.q.h, p.q.n,
-                                                           k2 + ci.b * p.k2.b + ci.hk * p.k2.h, p.k2.n, p.k2_bias);
-                form_product_tile<HD, kStreamRows, 128>(a_tile + L::kSmallTile, L::kSmallSlab, row, rho0, P.dw_log2, p.N,
-                                                           p.w2, p.halo2, d_o + ci.b * p.d_o.b + h * p.d_o.h, p.d_o.n,
-                                                           v2 + ci.b * p.v2.b + ci.hk * p.v2.h, p.v2.n, p.v2_bias);
+                const float* m_lse = (const float*)(smem + L::kMeta) + stage * 256;
+                const float* m_delta = m_lse + 128;
+                const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kColTileRows;
                 const int iq0 = (int)(rho0 >> P.dw_log2);
-                const int nq = max(1, kStreamRows >> P.dw_log2);
-                if (row < nq) {                              // LSE2 and Delta of the tile's queries
-                    const int i = iq0 + row;
-                    float* m_lse = (float*)(smem + L::kMeta) + stage * 128;
-                    const long li = ((long)ci.b * p.H + h) * p.N + min(i, p.N - 1);
-                    m_lse[row] = (i < p.N) ? P.lse2[li] : INFINITY;
-                    m_lse[64 + row] = (i < p.N) ? P.delta[li] : 0.f;
-                }
-                fence_proxy_async_smem();
-                mbar_arrive(&B.st_full[stage]);
-            };
-            for (int t = grp; t < nt && t < grp + kColStages; t += 2) form_tile(t);
-            for (int t = grp; t < nt; t += 2, ++n_mine) {
-                const int stage = (int)((g_base + t) % kColStages);
-                const float* m_lse = (const float*)(smem + L::kMeta) + stage * 128;
-                const float* m_delta = m_lse + 64;
-                const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kStreamRows;
-                const int iq0 = (int)(rho0 >> P.dw_log2);
-                mbar_wait(&B.sdp_ready[grp], n_mine & 1, wctx, 20);
+                mbar_wait(sdp_ready, g & 1, wctx, 20);
                 tc_fence_after();
 #pragma unroll 1
-                for (int c0 = 0; c0 < kStreamRows; c0 += 32) {
-                    uint32_t s[32], dp[32], pp[16], ds[16];
-                    tmem_ld32(tm_s[grp] + lane_addr + c0, s);
-                    tmem_ld32(tm_dp[grp] + lane_addr + c0, dp);
+                for (int cc = 0; cc < 64; cc += 16) {
+                    const int c0 = 64 * grp + cc;             // first of this chunk's 16 columns (virtual rows)
+                    uint32_t s[16], dp[16], pp[8], ds[8];
+                    tmem_ld16(tm_s + lane_addr + c0, s);
+                    tmem_ld16(tm_dp + lane_addr + c0, dp);
                     tmem_wait_ld();
-                    if (P.dw_log2 >= 5) {
-                        // the 32 columns belong to one query
+                    if (P.dw_log2 >= 4) {
+                        // the 16 columns belong to one query
                         const int i = (int)((rho0 + c0) >> P.dw_log2);
                         const bool valid = (jb <= i + p.halo1) && (jb >= i + p.halo1 - p.w1 + 1);
-                        softmax_bwd_chunk<true>(s, dp, 0, valid ? 0 : 1, valid ? 31 : 0, c2, m_lse[i - iq0], m_delta[i - iq0],
-                                                pp, ds);
+                        softmax_bwd_chunk<true, 16>(s, dp, 0, valid ? 0 : 1, valid ? 15 : 0, c2, m_lse[i - iq0], m_delta[i - iq0],
+                                                    pp, ds);
                     } else {
 #pragma unroll
-                        for (int e = 0; e < 32; e += 2) {
+                        for (int e = 0; e < 16; e += 2) {
                             float pv[2], dv[2];
 #pragma unroll
                             for (int x = 0; x < 2; ++x) {
@@ -351,13 +352,13 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             ds[e >> 1] = pack_bf16(dv[0], dv[1]);
                         }
                     }
-                    tmem_st16(tm_s[grp] + lane_addr + (c0 >> 1), pp);
-                    tmem_st16(tm_dp[grp] + lane_addr + (c0 >> 1), ds);
+                    // packed P^T / dS^T of columns [64g + cc, +16) go to tensor-memory columns 64g + cc/2 ...
+                    tmem_st8(tm_s + lane_addr + 64 * grp + (cc >> 1), pp);
+                    tmem_st8(tm_dp + lane_addr + 64 * grp + (cc >> 1), ds);
                 }
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(&B.pds_ready[grp]);
-                if (t + kColStages < nt) form_tile(t + kColStages);     // into the stage this tile is about to free
+                mbar_arrive(pds_ready);
             }
             g_base += nt;
             // epilogue: group 0 writes dV1, group 1 writes dK1 (times scale)
@@ -365,7 +366,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
             const sa_strides st = grp == 0 ? p.dv1 : p.dk1;
             const float mult = grp == 0 ? 1.f : p.scale;
             if (nt > 0) {
-                mbar_wait(B.acc_ready, n_items & 1, wctx, 21);
+                mbar_wait(acc_ready, n_items & 1, wctx, 21);
                 ++n_items;
                 tc_fence_after();
             }
@@ -392,56 +393,106 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
             }
             if (nt > 0) {
                 tc_fence_before();
-                mbar_arrive(B.acc_free);
+                mbar_arrive(acc_free);
             }
         }
-    } else if (warp == 8) {
+    } else if (warp < 16) {
+        // ---------------------------------------------------------------- producers: group 0 forms A, group 1 forms C
+        const int grp = (warp - 8) >> 2;
+        const int row = tid & 127;
+        uint32_t g_base = 0;
+        for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
+            const ColItem ci = col_item(P, it);
+            const int nt = ci.ntq * p.G;
+            // group 0 forms A = Q * (K2 + bias), group 1 forms C = dO * (V2 + bias) of a streamed tile
+            auto form_tile = [&](int t) {
+                const uint32_t g = g_base + t;
+                const int stage = (int)(g % kColStages);
+                const int h = ci.hk * p.G + t / ci.ntq;
+                const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kColTileRows;
+                uint8_t* tile = smem + L::kStream + (stage * 2 + grp) * L::kTile;
+                mbar_wait(&st_empty[stage], ((g / kColStages) & 1) ^ 1, wctx, 22);
+                if (grp == 0) {
+                    form_product_tile<HD, kColTileRows, 128>(tile, L::kSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2,
+                                                             q + ci.b * p.q.b + h * p.q.h, p.q.n,
+                                                             k2 + ci.b * p.k2.b + ci.hk * p.k2.h, p.k2.n, p.k2_bias);
+                    // LSE2 and Delta of the tile's queries
+                    const int iq0 = (int)(rho0 >> P.dw_log2);
+                    const int nq = max(1, kColTileRows >> P.dw_log2);
+                    if (row < nq) {
+                        const int i = iq0 + row;
+                        float* m_lse = (float*)(smem + L::kMeta) + stage * 256;
+                        const long li = ((long)ci.b * p.H + h) * p.N + min(i, p.N - 1);
+                        m_lse[row] = (i < p.N) ? P.lse2[li] : INFINITY;
+                        m_lse[128 + row] = (i < p.N) ? P.delta[li] : 0.f;
+                    }
+                } else {
+                    form_product_tile<HD, kColTileRows, 128>(tile, L::kSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2,
+                                                             d_o + ci.b * p.d_o.b + h * p.d_o.h, p.d_o.n,
+                                                             v2 + ci.b * p.v2.b + ci.hk * p.v2.h, p.v2.n, p.v2_bias);
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(&st_full[stage]);
+            };
+            for (int t = 0; t < nt; ++t) form_tile(t);
+            g_base += nt;
+        }
+    } else if (warp == 16) {
         // ---------------------------------------------------------------- MMA issuer
-        reg_dealloc<72>();
+        reg_dealloc<80>();
         if (lane == 0) {
-            uint32_t nb[2] = {0, 0}, g_base = 0, n_items = 0;
-            const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false);
-            const uint32_t k1s = smem_base + L::kStat0, v1s = smem_base + L::kStat1;
+            uint32_t g_base = 0, n_items = 0;
+            const uint32_t idesc_sd = make_idesc(128, kColTileRows, false, false);
+            const uint32_t idesc_acc = make_idesc(128, HD, false, true);
+            const uint64_t d_k1 = desc_kmajor(smem_base + L::kK1, 0), d_v1 = desc_kmajor(smem_base + L::kV1, 0);
             for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
                 const ColItem ci = col_item(P, it);
                 const int nt = ci.ntq * p.G;
                 if (nt == 0) continue;
-                mbar_wait(B.stat_full, n_items & 1, wctx, 23);
-                if (n_items > 0) mbar_wait(B.acc_free, (n_items - 1) & 1, wctx, 24);
+                mbar_wait(stat_full, n_items & 1, wctx, 23);
+                if (n_items > 0) mbar_wait(acc_free, (n_items - 1) & 1, wctx, 24);
                 tc_fence_after();
-                for (int t = 0; t <= nt; ++t) {
-                    if (t < nt) {
-                        const uint32_t g = g_base + t;
-                        const int stage = (int)(g % kColStages), b = t & 1;
-                        const uint32_t a_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, c_t = a_t + L::kSmallTile;
-                        mbar_wait(&B.st_full[stage], (g / kColStages) & 1, wctx, 25);
-                        tc_fence_after();
-                        issue_sdp<HD>(tm_s[b], tm_dp[b], k1s, v1s, a_t, c_t, idesc_full);
-                        tc_commit(&B.sdp_ready[b]);
+                for (int t = 0; t < nt; ++t) {
+                    const uint32_t g = g_base + t;
+                    const int stage = (int)(g % kColStages);
+                    const uint32_t a_t = smem_base + L::kStream + stage * 2 * L::kTile, c_t = a_t + L::kTile;
+                    const uint64_t d_a = desc_kmajor(a_t, 0), d_c = desc_kmajor(c_t, 0);
+                    const uint64_t d_am = desc_mnmajor(a_t, L::kSlab), d_cm = desc_mnmajor(c_t, L::kSlab);
+                    mbar_wait(&st_full[stage], (g / kColStages) & 1, wctx, 25);
+                    tc_fence_after();
+                    // S^T = K1 A^T,  dP^T = V1 C^T
+#pragma unroll
+                    for (int kk = 0; kk < HD / 16; ++kk) {
+                        const uint32_t off = ((kk >> 2) * L::kSlab + (kk & 3) * 32) >> 4;
+                        mma_ss(tm_s, d_k1 + off, d_a + off, idesc_sd, kk > 0);
                     }
-                    if (t >= 1) {
-                        const int tp = t - 1;
-                        const uint32_t g = g_base + tp;
-                        const int stage = (int)(g % kColStages), b = tp & 1;
-                        const uint32_t a_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, c_t = a_t + L::kSmallTile;
-                        mbar_wait(&B.pds_ready[b], nb[b] & 1, wctx, 26);
-                        ++nb[b];
-                        tc_fence_after();
-                        // dV1 += P^T-tile * C-tile ; dK1 += dS^T-tile * A-tile
-                        issue_acc<HD>(tm_dv1, tm_dk1, tm_s[b], tm_dp[b], a_t, c_t, kStreamRows / 16, tp > 0);
-                        tc_commit(&B.st_empty[stage]);
+#pragma unroll
+                    for (int kk = 0; kk < HD / 16; ++kk) {
+                        const uint32_t off = ((kk >> 2) * L::kSlab + (kk & 3) * 32) >> 4;
+                        mma_ss(tm_dp, d_v1 + off, d_c + off, idesc_sd, kk > 0);
                     }
+                    tc_commit(sdp_ready);
+                    mbar_wait(pds_ready, g & 1, wctx, 26);
+                    tc_fence_after();
+                    // dV1 += P^T-tile C-tile,  dK1 += dS^T-tile A-tile   (K = 128 virtual rows: 8 steps of 16)
+#pragma unroll
+                    for (int kk = 0; kk < kColTileRows / 16; ++kk)
+                        mma_ts(tm_dv1, tm_s + (kk >> 2) * 64 + (kk & 3) * 8, d_cm + kk * (2048 >> 4), idesc_acc, t > 0 || kk > 0);
+#pragma unroll
+                    for (int kk = 0; kk < kColTileRows / 16; ++kk)
+                        mma_ts(tm_dk1, tm_dp + (kk >> 2) * 64 + (kk & 3) * 8, d_am + kk * (2048 >> 4), idesc_acc, t > 0 || kk > 0);
+                    tc_commit(&st_empty[stage]);
                 }
-                tc_commit(B.acc_ready);
-                tc_commit(B.stat_empty);
+                tc_commit(acc_ready);
+                tc_commit(stat_empty);
                 g_base += nt;
                 ++n_items;
             }
         }
         __syncwarp();
-    } else if (warp == 9) {
+    } else if (warp == 17) {
         // ---------------------------------------------------------------- TMA: the block's K1 / V1 rows
-        reg_dealloc<72>();
+        reg_dealloc<80>();
         if (lane == 0) {
             prefetch_tensormap(&map_k1);
             prefetch_tensormap(&map_v1);
@@ -449,23 +500,23 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
             for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
                 const ColItem ci = col_item(P, it);
                 if (ci.ntq == 0) continue;
-                mbar_wait(B.stat_empty, (n & 1) ^ 1, wctx, 27);
-                mbar_arrive_expect_tx(B.stat_full, 2 * L::kBigTile);
+                mbar_wait(stat_empty, (n & 1) ^ 1, wctx, 27);
+                mbar_arrive_expect_tx(stat_full, 2 * L::kTile);
 #pragma unroll
                 for (int sl = 0; sl < L::kSlabs; ++sl) {
-                    tma_load_4d(smem + L::kStat0 + sl * L::kBigSlab, &map_k1, B.stat_full, sl * 64, ci.j0, ci.hk, ci.b);
-                    tma_load_4d(smem + L::kStat1 + sl * L::kBigSlab, &map_v1, B.stat_full, sl * 64, ci.j0, ci.hk, ci.b);
+                    tma_load_4d(smem + L::kK1 + sl * L::kSlab, &map_k1, stat_full, sl * 64, ci.j0, ci.hk, ci.b);
+                    tma_load_4d(smem + L::kV1 + sl * L::kSlab, &map_v1, stat_full, sl * 64, ci.j0, ci.hk, ci.b);
                 }
                 ++n;
             }
         }
         __syncwarp();
     } else {
-        reg_dealloc<72>();
+        reg_dealloc<80>();
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 8) {
+    if (warp == 16) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
@@ -1037,14 +1088,14 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         const long grid = P.num_col_items < sm_count ? P.num_col_items : sm_count;
         if (k.D == 128) {
             auto kern = bwd_col_kernel<128>;
-            using LC = BwdSmem<128, kColStages>;
+            using LC = ColSmem<128>;
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LC::kAlloc) != cudaSuccess)
                 return SA_ERR_LAUNCH;
             kern<<<(unsigned)grid, kColThreads, LC::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
                                                                              (__nv_bfloat16*)dk1, (__nv_bfloat16*)dv1);
         } else {
             auto kern = bwd_col_kernel<64>;
-            using LC = BwdSmem<64, kColStages>;
+            using LC = ColSmem<64>;
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LC::kAlloc) != cudaSuccess)
                 return SA_ERR_LAUNCH;
             kern<<<(unsigned)grid, kColThreads, LC::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
