@@ -360,6 +360,54 @@ __device__ __forceinline__ void form_product_tile(uint8_t* tile, int slab_bytes,
     }
 }
 
+
+// Same result as form_product_tile for a 128-row tile whose queries are aligned to it (DW = 1 << DWLOG
+// delta slots per query, 128 / DW queries per tile), but every y row (K2 or V2) is loaded once and
+// used for all the queries it pairs with: consecutive queries share all but one of their DW rows.
+// Window row w (0 <= w < DW + nq - 1) is y row  kb = i0 + halo2 - (DW-1) + w ; it meets query x at
+// delta = DW - 1 + x - w.  One round of loads per tile: NQ chunks of x and PASSES chunks of y.
+template <int HD, int DWLOG>
+__device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab_bytes, int t, int i0, int n_q, int w2,
+                                                         int halo2, const __nv_bfloat16* x, int64_t xs,
+                                                         const __nv_bfloat16* y, int64_t ys, float bias) {
+    constexpr int C = HD / 8;
+    constexpr int RPP = 128 / C;                  // window rows per pass
+    constexpr int DW = 1 << DWLOG;
+    constexpr int NQ = 128 / DW;
+    constexpr int NWIN = DW + NQ - 1;
+    constexpr int PASSES = (NWIN + RPP - 1) / RPP;
+    const int c = t % C, pr = t / C;
+    const int kb_first = i0 + halo2 - (DW - 1);
+    uint4 xa[NQ], ya[PASSES];
+#pragma unroll
+    for (int q2 = 0; q2 < NQ; ++q2) {
+        xa[q2] = make_uint4(0, 0, 0, 0);
+        if (i0 + q2 < n_q) xa[q2] = __ldg((const uint4*)(x + (int64_t)(i0 + q2) * xs) + c);
+    }
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+        const int w = pr + k * RPP;
+        const int kb = kb_first + w;
+        ya[k] = make_uint4(0, 0, 0, 0);
+        if (w < NWIN && kb >= 0) ya[k] = __ldg((const uint4*)(y + (int64_t)kb * ys) + c);
+    }
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) {
+        const int w = pr + k * RPP;
+        const int kb = kb_first + w;
+#pragma unroll
+        for (int q2 = 0; q2 < NQ; ++q2) {
+            const int dlt = DW - 1 + q2 - w;
+            if (dlt < 0 || dlt >= DW) continue;
+            const int r = q2 * DW + dlt;
+            uint4 out = make_uint4(0, 0, 0, 0);
+            if (i0 + q2 < n_q && dlt < w2 && kb >= 0)
+                out = (bias == 0.f) ? mul_chunk_nobias(xa[q2], ya[k]) : mul_chunk(xa[q2], ya[k], bias);
+            *(uint4*)(tile + (c >> 3) * slab_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = out;
+        }
+    }
+}
+
 // Sum over the 32 lanes of a warp of CW values per lane; afterwards lane L holds the total of
 // value (L % CW) in v[0].  A halving exchange: each step a lane keeps one half of its values and
 // adds the partner's copy of that half, 31 shuffles for 32 values.

@@ -412,12 +412,22 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kColTileRows;
                 uint8_t* tile = smem + L::kStream + (stage * 2 + grp) * L::kTile;
                 mbar_wait(&st_empty[stage], ((g / kColStages) & 1) ^ 1, wctx, 22);
+                const __nv_bfloat16* xb = grp == 0 ? q + ci.b * p.q.b + h * p.q.h : d_o + ci.b * p.d_o.b + h * p.d_o.h;
+                const int64_t xs = grp == 0 ? p.q.n : p.d_o.n;
+                const __nv_bfloat16* yb = grp == 0 ? k2 + ci.b * p.k2.b + ci.hk * p.k2.h : v2 + ci.b * p.v2.b + ci.hk * p.v2.h;
+                const int64_t ys = grp == 0 ? p.k2.n : p.v2.n;
+                const float bias = grp == 0 ? p.k2_bias : p.v2_bias;
+                const int iq0 = (int)(rho0 >> P.dw_log2);
+                switch (P.dw_log2) {     // whole queries per tile: share the K2 / V2 rows between them
+                    case 4: form_product_tile_shared<HD, 4>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
+                    case 5: form_product_tile_shared<HD, 5>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
+                    case 6: form_product_tile_shared<HD, 6>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
+                    default:
+                        form_product_tile<HD, kColTileRows, 128>(tile, L::kSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2, xb, xs,
+                                                                 yb, ys, bias);
+                }
                 if (grp == 0) {
-                    form_product_tile<HD, kColTileRows, 128>(tile, L::kSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2,
-                                                             q + ci.b * p.q.b + h * p.q.h, p.q.n,
-                                                             k2 + ci.b * p.k2.b + ci.hk * p.k2.h, p.k2.n, p.k2_bias);
                     // LSE2 and Delta of the tile's queries
-                    const int iq0 = (int)(rho0 >> P.dw_log2);
                     const int nq = max(1, kColTileRows >> P.dw_log2);
                     if (row < nq) {
                         const int i = iq0 + row;
@@ -426,10 +436,6 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         m_lse[row] = (i < p.N) ? P.lse2[li] : INFINITY;
                         m_lse[128 + row] = (i < p.N) ? P.delta[li] : 0.f;
                     }
-                } else {
-                    form_product_tile<HD, kColTileRows, 128>(tile, L::kSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2,
-                                                             d_o + ci.b * p.d_o.b + h * p.d_o.h, p.d_o.n,
-                                                             v2 + ci.b * p.v2.b + ci.hk * p.v2.h, p.v2.n, p.v2_bias);
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(&st_full[stage]);
