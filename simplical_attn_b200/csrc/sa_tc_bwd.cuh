@@ -323,20 +323,37 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const int iq0 = (int)(rho0 >> P.dw_log2);
                 mbar_wait(sdp_ready, g & 1, wctx, 20);
                 tc_fence_after();
-#pragma unroll 1
-                for (int cc = 0; cc < 64; cc += 16) {
-                    const int c0 = 64 * grp + cc;             // first of this chunk's 16 columns (virtual rows)
-                    uint32_t s[16], dp[16], pp[8], ds[8];
-                    tmem_ld16(tm_s + lane_addr + c0, s);
-                    tmem_ld16(tm_dp + lane_addr + c0, dp);
-                    tmem_wait_ld();
-                    if (P.dw_log2 >= 4) {
-                        // the 16 columns belong to one query
+                if (P.dw_log2 >= 4) {
+                    // 16 columns (virtual rows) at a time, each chunk within one query; the next chunk's
+                    // tensor-memory loads are in flight while the current one is processed
+                    uint32_t s[2][16], dp[2][16];
+                    tmem_ld16(tm_s + lane_addr + 64 * grp, s[0]);
+                    tmem_ld16(tm_dp + lane_addr + 64 * grp, dp[0]);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const int c0 = 64 * grp + 16 * k;
+                        tmem_wait_ld();
+                        if (k + 1 < 4) {
+                            tmem_ld16(tm_s + lane_addr + c0 + 16, s[(k + 1) & 1]);
+                            tmem_ld16(tm_dp + lane_addr + c0 + 16, dp[(k + 1) & 1]);
+                        }
                         const int i = (int)((rho0 + c0) >> P.dw_log2);
                         const bool valid = (jb <= i + p.halo1) && (jb >= i + p.halo1 - p.w1 + 1);
-                        softmax_bwd_chunk<true, 16>(s, dp, 0, valid ? 0 : 1, valid ? 15 : 0, c2, m_lse[i - iq0], m_delta[i - iq0],
-                                                    pp, ds);
-                    } else {
+                        uint32_t pp[8], ds[8];
+                        softmax_bwd_chunk<true, 16>(s[k & 1], dp[k & 1], 0, valid ? 0 : 1, valid ? 15 : 0, c2, m_lse[i - iq0],
+                                                    m_delta[i - iq0], pp, ds);
+                        // packed P^T / dS^T of columns [64g + 16k, +16) go to tensor-memory columns 64g + 8k ...
+                        tmem_st8(tm_s + lane_addr + 64 * grp + 8 * k, pp);
+                        tmem_st8(tm_dp + lane_addr + 64 * grp + 8 * k, ds);
+                    }
+                } else {
+#pragma unroll 1
+                    for (int cc = 0; cc < 64; cc += 16) {
+                        const int c0 = 64 * grp + cc;
+                        uint32_t s[16], dp[16], pp[8], ds[8];
+                        tmem_ld16(tm_s + lane_addr + c0, s);
+                        tmem_ld16(tm_dp + lane_addr + c0, dp);
+                        tmem_wait_ld();
 #pragma unroll
                         for (int e = 0; e < 16; e += 2) {
                             float pv[2], dv[2];
@@ -351,10 +368,9 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             pp[e >> 1] = pack_bf16(pv[0], pv[1]);
                             ds[e >> 1] = pack_bf16(dv[0], dv[1]);
                         }
+                        tmem_st8(tm_s + lane_addr + 64 * grp + (cc >> 1), pp);
+                        tmem_st8(tm_dp + lane_addr + 64 * grp + (cc >> 1), ds);
                     }
-                    // packed P^T / dS^T of columns [64g + cc, +16) go to tensor-memory columns 64g + cc/2 ...
-                    tmem_st8(tm_s + lane_addr + 64 * grp + (cc >> 1), pp);
-                    tmem_st8(tm_dp + lane_addr + 64 * grp + (cc >> 1), ds);
                 }
                 tmem_wait_st();
                 tc_fence_before();
