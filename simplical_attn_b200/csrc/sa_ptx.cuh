@@ -33,14 +33,17 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// One probe of the barrier.  The suspend-time hint lets the hardware park the warp until the phase
+// completes (it wakes at once when it does) instead of spinning through issue slots that the
+// working warps of the same scheduler need.
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(20000u)
         : "memory");
     return ok != 0;
 }
@@ -361,17 +364,18 @@ __device__ __forceinline__ void form_product_tile(uint8_t* tile, int slab_bytes,
 }
 
 
+
 // Same result as form_product_tile for a 128-row tile whose queries are aligned to it (DW = 1 << DWLOG
 // delta slots per query, 128 / DW queries per tile), but every y row (K2 or V2) is loaded once and
 // used for all the queries it pairs with: consecutive queries share all but one of their DW rows.
 // Window row w (0 <= w < DW + nq - 1) is y row  kb = i0 + halo2 - (DW-1) + w ; it meets query x at
 // delta = DW - 1 + x - w.  One round of loads per tile: NQ chunks of x and PASSES chunks of y.
-template <int HD, int DWLOG>
+template <int HD, int DWLOG, int NTHREADS = 128>
 __device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab_bytes, int t, int i0, int n_q, int w2,
                                                          int halo2, const __nv_bfloat16* x, int64_t xs,
                                                          const __nv_bfloat16* y, int64_t ys, float bias) {
     constexpr int C = HD / 8;
-    constexpr int RPP = 128 / C;                  // window rows per pass
+    constexpr int RPP = NTHREADS / C;             // window rows per pass
     constexpr int DW = 1 << DWLOG;
     constexpr int NQ = 128 / DW;
     constexpr int NWIN = DW + NQ - 1;

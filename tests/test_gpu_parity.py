@@ -218,3 +218,43 @@ def test_bad_arguments_raise():
     from simplical_attn_b200._abi import SimplicialAttnError
     with pytest.raises(SimplicialAttnError):
         sab.two_simplicial_attention(ins[0], ins[1], ins[2], ins[3], ins[4], 0, 8)
+
+
+@pytest.mark.parametrize("w1", [128, 256, 512, 1024])
+@pytest.mark.parametrize("w2", [16, 32, 64])
+def test_window_sweep_tensor_core_vs_general(w1, w2):
+    """The window sweep of the batch x head-parallel configuration (w1 in {128..1024} x w2 in {16,32,64},
+    D=128) at a reduced batch and length: both kernel families on the same bf16 inputs."""
+    B, N, H, Hkv, D = 1, 1536, 2, 2, 128
+    q, k1, k2, v1, v2, do = so.make_inputs(B, N, H, Hkv, D, seed=w1 + w2)
+    cfg = dict(w1=w1, w2=w2, scale=1.0 / math.sqrt(D), k2_bias=0.0, v2_bias=0.0)
+    ins = dict(q=q, k1=k1, k2=k2, v1=v1, v2=v2, do=do)
+    o_t, lse_t, g_t = _run(ins, cfg, "tcgen05")
+    o_g, lse_g, g_g = _run(ins, cfg, "general")
+    assert float((o_t.float() - o_g.float()).abs().max()) <= 3e-2
+    assert float((lse_t - lse_g).abs().max()) <= 1e-2
+    for nm, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), g_t, g_g):
+        assert so.rel_l2(a.float().cpu(), b.float().cpu()) <= TOL_G_BF16, nm
+
+
+def test_grouped_heads_full_size():
+    """The grouped-head configuration (B1, 32 query heads on 2 KV heads, N=16384, D=128, w 512/32): forward
+    row slices against the C loop oracle, all five gradients against the general kernels (which sum
+    the 16 query heads of a group inside one warp, in a fixed order)."""
+    B, N, H, Hkv, D, w1, w2 = 1, 16384, 32, 2, 128, 512, 32
+    scale = 1.0 / math.sqrt(D)
+    q, k1, k2, v1, v2, do = so.make_inputs(B, N, H, Hkv, D)
+    cfg = dict(w1=w1, w2=w2, scale=scale, k2_bias=0.0, v2_bias=0.0)
+    ins = dict(q=q, k1=k1, k2=k2, v1=v1, v2=v2, do=do)
+    o_t, lse_t, g_t = _run(ins, cfg, "tcgen05")
+    assert all(bool(torch.isfinite(t.float()).all()) for t in (o_t, *g_t))
+    for lo, hi in ((0, 24), (8190, 8200), (16376, 16384)):
+        ro, rl = c_oracle.forward(q, k1, k2, v1, v2, w1, w2, scale, row_begin=lo, row_end=hi)
+        assert float((o_t[:, lo:hi].float().cpu() - ro[:, lo:hi]).abs().max()) <= TOL_O_BF16
+        assert float((lse_t[:, :, lo:hi].cpu() - rl[:, :, lo:hi]).abs().max()) <= 2e-2
+    t = {k: v.to(DEV).to(torch.bfloat16) for k, v in ins.items()}
+    g_g = sab.two_simplicial_attn_bwd(t["q"], t["k1"], t["k2"], t["v1"], t["v2"], o_t, lse_t, t["do"], w1, w2, scale,
+                                      algo="general")
+    torch.cuda.synchronize()
+    for nm, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), g_t, g_g):
+        assert so.rel_l2(a.float().cpu(), b.float().cpu()) <= TOL_G_BF16, nm

@@ -54,7 +54,7 @@ def test_sharded_matches_single_gpu(tmp_path):
         pytest.skip("needs two GPUs")
     import simplical_attn_b200 as sab
     from oracle import simplicial_oracle as so
-    cfg = (1, 2048, 4, 2, 128, 512, 32)
+    cfg = (1, 4096, 4, 2, 128, 1024, 64)       # the long-sequence configuration's windows
     world = 2
     mp.spawn(_worker, args=(world, _free_port(), cfg, str(tmp_path)), nprocs=world, join=True)
     B, N, H, Hkv, D, w1, w2 = cfg
