@@ -762,25 +762,34 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     const int wq = row >> 5;
                     float* dq_part = scr_a;                              // [4 warps][HD]
                     const int slot = row_valid ? kb % max(ring_rows, 1) : 0;
+                    // Rows that are not valid (delta >= w2, K2 row before the buffer, query past the end) have
+                    // P = dS = 0, hence exact zeros in U and G: they need no masking in the sums below.
 #pragma unroll 1
                     for (int ph = 0; ph < 4; ++ph) {
                         const int c = (wq + ph) & 3;
                         SA_PROF_T0(t_p0);
-                        uint32_t yw[CW / 2], xw[CW / 2];
+                        uint32_t yw[CW / 2], xw[CW / 2], g[CW];
                         load_bf16_words<CW>(y_row + c * CW, yw);
                         if (grp == 0) load_bf16_words<CW>(k2_row + c * CW, xw);
-                        uint32_t g[CW];
                         tmem_ld_cw<CW>(acc + c * CW, g);
                         SA_PROF_ADD(50 + 4 * grp, t_p0);
                         SA_PROF_T0(t_p1);
                         if (grp == 0 && dq != nullptr) {
                             float v[CW];
+                            if (p.k2_bias == 0.f) {
 #pragma unroll
-                            for (int e = 0; e < CW; e += 2) {
-                                v[e] = row_valid ? __uint_as_float(g[e]) * (bf16_lo(xw[e >> 1]) + p.k2_bias) * mult : 0.f;
-                                v[e + 1] = row_valid ? __uint_as_float(g[e + 1]) * (bf16_hi(xw[e >> 1]) + p.k2_bias) * mult : 0.f;
+                                for (int e = 0; e < CW; e += 2) {
+                                    v[e] = __uint_as_float(g[e]) * bf16_lo(xw[e >> 1]);
+                                    v[e + 1] = __uint_as_float(g[e + 1]) * bf16_hi(xw[e >> 1]);
+                                }
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < CW; e += 2) {
+                                    v[e] = __uint_as_float(g[e]) * (bf16_lo(xw[e >> 1]) + p.k2_bias);
+                                    v[e + 1] = __uint_as_float(g[e + 1]) * (bf16_hi(xw[e >> 1]) + p.k2_bias);
+                                }
                             }
-                            const float tot = warp_transpose_reduce<CW>(v, lane);
+                            const float tot = warp_transpose_reduce<CW>(v, lane) * mult;
                             if (lane < CW) dq_part[wq * HD + c * CW + lane] = tot;
                         }
                         SA_PROF_ADD(51 + 4 * grp, t_p1);
@@ -792,8 +801,8 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             for (int e = 0; e < CW; ++e) acc_r[e] = ring[ring_index<HD>(slot, c * CW + e)];
 #pragma unroll
                             for (int e = 0; e < CW; e += 2) {
-                                acc_r[e] += __uint_as_float(g[e]) * bf16_lo(yw[e >> 1]) * mult;
-                                acc_r[e + 1] += __uint_as_float(g[e + 1]) * bf16_hi(yw[e >> 1]) * mult;
+                                acc_r[e] = fmaf(__uint_as_float(g[e]) * mult, bf16_lo(yw[e >> 1]), acc_r[e]);
+                                acc_r[e + 1] = fmaf(__uint_as_float(g[e + 1]) * mult, bf16_hi(yw[e >> 1]), acc_r[e + 1]);
                             }
 #pragma unroll
                             for (int e = 0; e < CW; ++e) ring[ring_index<HD>(slot, c * CW + e)] = acc_r[e];
