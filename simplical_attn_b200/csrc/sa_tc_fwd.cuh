@@ -314,32 +314,41 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                     }
                 };
                 if (full) {
-                    // single pass: the whole row of S sits in registers
-                    uint32_t v[4][32];
-#pragma unroll
-                    for (int cch = 0; cch < 4; ++cch) tmem_ld32(s_addr + 32 * cch, v[cch]);
-                    tmem_wait_ld();
+                    // two passes over tensor memory, 32 columns at a time, the next chunk's load in flight
+                    // while the current one is processed (keeps the live registers at two chunks)
+                    uint32_t v[2][32];
                     float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-#pragma unroll
-                        for (int cch = 0; cch < 4; ++cch) mx[cch] = fmaxf(mx[cch], __uint_as_float(v[cch][e]));
-                    }
-                    update_max(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c2);
-                    float ls[4] = {0.f, 0.f, 0.f, 0.f};
+                    tmem_ld32(s_addr, v[0]);
 #pragma unroll
                     for (int cch = 0; cch < 4; ++cch) {
+                        tmem_wait_ld();
+                        if (cch + 1 < 4) tmem_ld32(s_addr + 32 * (cch + 1), v[(cch + 1) & 1]);
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4) {
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) mx[x] = fmaxf(mx[x], __uint_as_float(v[cch & 1][e + x]));
+                        }
+                    }
+                    tmem_ld32(s_addr, v[0]);                  // issued before the (rare) rescale so its latency overlaps
+                    update_max(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c2);
+                    float ls[2] = {0.f, 0.f};
+#pragma unroll
+                    for (int cch = 0; cch < 4; ++cch) {
+                        tmem_wait_ld();
+                        if (cch + 1 < 4) tmem_ld32(s_addr + 32 * (cch + 1), v[(cch + 1) & 1]);
                         uint32_t pk[16];
 #pragma unroll
                         for (int e = 0; e < 32; e += 2) {
-                            const float p0 = ex2(fmaf(__uint_as_float(v[cch][e]), c2, -m));
-                            const float p1 = ex2(fmaf(__uint_as_float(v[cch][e + 1]), c2, -m));
-                            ls[cch] += p0 + p1;
+                            const float p0 = ex2(fmaf(__uint_as_float(v[cch & 1][e]), c2, -m));
+                            const float p1 = ex2(fmaf(__uint_as_float(v[cch & 1][e + 1]), c2, -m));
+                            ls[0] += p0;
+                            ls[1] += p1;
                             pk[e >> 1] = pack_bf16(p0, p1);
                         }
+                        // chunk cch of P (16 packed columns) lands on S columns that have been read already
                         tmem_st16(s_addr + 16 * cch, pk);
                     }
-                    lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
+                    lsum = ls[0] + ls[1];
                 } else {
                     // pass 1: row maximum of the valid columns
                     float tmax = -INFINITY;
