@@ -10,9 +10,10 @@ N=8192, D=128, w1=512, w2=32, bf16, forward + backward; with N GPUs each rank ta
 
 One step = one forward and one backward over the rank's batch.  `value` is whole-job TFLOP/s with
 inputs resident in HBM, counting 16*B*H*N*w1*w2*D FLOPs per step (2 contractions forward, 6
-backward, 2*B*H*N*w1*w2*D each).  `e2e` is the same metric through the public call with pinned host
-buffers: host->device copies of the six inputs and device->host copies of O and the five
-gradients inside the timed region.  `roofline` describes the dominant kernel; `cpu_baseline`
+backward, 2*B*H*N*w1*w2*D each).  `e2e` is the same metric through the library's host-tensor call
+(`HostPipeline.forward_backward`: pinned host buffers in and out): host->device copies of the six
+inputs and device->host copies of O and the five gradients inside the timed region, overlapped with
+the kernels by batch chunks.  `roofline` describes the dominant kernel; `cpu_baseline`
 times the C loop oracle on the host cores on a bounded sample of the same workload.
 
 `--impl reference` times the reference's algorithm on the host cores (the C restatement of its
@@ -222,17 +223,14 @@ def main():
         grads = sab.two_simplicial_attn_bwd(q, k1, k2, v1, v2, o, lse, do, w1, w2, scale)
         return o, grads
 
-    host_out = [torch.empty_like(h) for h in (host[0], host[0], host[1], host[2], host[3], host[4])]
+    host_out = [torch.empty_like(h).pin_memory() for h in (host[0], host[0], host[1], host[2], host[3], host[4])]
+    from simplical_attn_b200.host_pipeline import HostPipeline
+    pipe = HostPipeline(device, chunk=2)
 
     def step_e2e():
-        d = [t.to(device, non_blocking=True) for t in host]
-        dq_in = d[0].requires_grad_(True)
-        kv = [t.requires_grad_(True) for t in d[1:5]]
-        o = sab.two_simplicial_attention(dq_in, *kv, w1, w2, scale)
-        o.backward(d[5])
-        outs = [o.detach(), dq_in.grad] + [t.grad for t in kv]
-        for dst, src in zip(host_out, outs):
-            dst.copy_(src, non_blocking=True)
+        # the library's host-tensor entry point: pinned host inputs in, pinned host results out; the
+        # uploads, kernels and downloads of successive batch chunks overlap on three streams
+        pipe.forward_backward(*host, w1, w2, scale, out=host_out)
 
     def barrier():
         if dist is not None:
