@@ -183,6 +183,8 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="override the global batch (profiling on a small case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--sweep", action="store_true",
+                    help="also time the window sweep w1 in {128,256,512,1024} x w2 in {16,32,64} (adds a 'sweep' key)")
     args = ap.parse_args()
     cfg = dict(WORKLOAD)
     if args.batch is not None:
@@ -288,6 +290,18 @@ def main():
                                                             need=(True, False, True, False, True)), reps)
     del o, lse
 
+    sweep = None
+    if args.sweep:
+        sweep = []
+        for sw1 in (128, 256, 512, 1024):
+            for sw2 in (16, 32, 64):
+                def one():
+                    o_, lse_ = sab.two_simplicial_attn_fwd_kernel(q, k1, k2, v1, v2, sw1, sw2, scale)
+                    sab.two_simplicial_attn_bwd(q, k1, k2, v1, v2, o_, lse_, do, sw1, sw2, scale)
+                ms = timed(one, 2, 1)
+                u = flops_unit(cfg["B"], cfg["H"], cfg["N"], D, sw1, sw2)
+                sweep.append({"w1": sw1, "w2": sw2, "ms_per_step": ms, "tflops": 8.0 * u / (ms * 1e-3) / 1e12})
+
     ms_e2e = None
     if not args.no_e2e:
         ms_e2e = timed(step_e2e, max(1, min(args.steps, 3)), 1)
@@ -337,6 +351,11 @@ def main():
             "frac_of_peak": {"measured_sustained": value / world / peak, "nominal_2250": value / world / 2250.0},
             "clocks": clocks, "gpu_launches": launches, "roofline": roof,
         }
+        if sweep is not None:
+            for pt in sweep:
+                pt["frac_of_measured_peak"] = pt["tflops"] / world / peak
+                pt["frac_of_nominal_2250"] = pt["tflops"] / world / 2250.0
+            line["sweep"] = sweep
         if ms_e2e is not None:
             h2d = sum(t.numel() * t.element_size() for t in host)
             d2h = sum(t.numel() * t.element_size() for t in host_out)

@@ -434,6 +434,23 @@ __device__ __forceinline__ float warp_transpose_reduce(float (&v)[CW], int lane)
     return v[0];
 }
 
+
+// The same exchange within each half of the warp (lanes 0-15 and 16-31 separately), for 16 values:
+// lane L ends up with the total, over its 16-lane half, of value (L % 16).
+__device__ __forceinline__ float half_warp_transpose_reduce16(float (&v)[16], int lane) {
+#pragma unroll
+    for (int s = 8; s >= 1; s >>= 1) {
+        const bool upper = (lane & s) != 0;
+#pragma unroll
+        for (int j = 0; j < s; ++j) {
+            const float send = upper ? v[j] : v[j + s];
+            const float keep = upper ? v[j + s] : v[j];
+            v[j] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+        }
+    }
+    return v[0];
+}
+
 // Byte offset of element (row, col) inside a 128-byte-swizzled [rows x 64] bf16 slab.
 __device__ __forceinline__ uint32_t swz128_offset(int row, int col) {
     return (uint32_t)row * 128u + ((((uint32_t)col >> 3) ^ ((uint32_t)row & 7u)) << 4) + (((uint32_t)col & 7u) << 1);

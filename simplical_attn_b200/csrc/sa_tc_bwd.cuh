@@ -617,27 +617,27 @@ __device__ __forceinline__ int ring_index(int slot, int col) {
     return slot * HD + ((col & ~31) | ((col ^ slot) & 31));
 }
 
-template <int HD>
+template <int HD, int NS, bool TWOQ>
 __global__ void __launch_bounds__(kRowThreads, 1)
 bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
                const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
                const __nv_bfloat16* __restrict__ k2, const __nv_bfloat16* __restrict__ v2,
                const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dq, int need_kv2, int ring_rows) {
-    using L = BwdSmem<HD, kRowStages>;
+    using L = BwdSmem<HD, NS>;
     using namespace ptx;
     constexpr int CW = HD / 4;                            // epilogue chunk width
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
     const KParams& p = P.k;
-    const BwdBars B = bwd_bars<kRowStages>((uint64_t*)(smem + L::kBars));
+    const BwdBars B = bwd_bars<NS>((uint64_t*)(smem + L::kBars));
     uint32_t* tmem_slot = (uint32_t*)(smem + L::kMisc);
     volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
     const WaitCtx wctx{abort_flag, P.status};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int s = 0; s < kRowStages; ++s) {
+        for (int s = 0; s < NS; ++s) {
             mbar_init(&B.st_full[s], 1);
             mbar_init(&B.st_empty[s], 1);
         }
@@ -755,12 +755,15 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 mbar_wait(B.acc_ready, n_units & 1, wctx, 31);
                 tc_fence_after();
                 SA_PROF_T0(t_epi);
-                if (P.dw_log2 >= 5 && (ring_rows > 0 || !need_kv2)) {
-                    // ---- a warp holds 32 consecutive deltas of one query: its lanes own distinct K2 rows.
-                    // Warp w works on column chunk (w + phase) % 4, so no two warps touch the same ring
-                    // columns at the same time; the delta sum for dQ is a register exchange inside the warp.
+                if ((TWOQ ? P.dw_log2 == 4 : P.dw_log2 >= 5) && (ring_rows > 0 || !need_kv2)) {
+                    // ---- a warp holds 32 consecutive deltas of one query (DW >= 32) or all 16 deltas of two
+                    // queries (DW = 16): within a query its lanes own distinct K2 rows.  Warp w works on
+                    // column chunk (w + phase) % 4, so no two warps touch the same ring columns at the same
+                    // time; the delta sum for dQ is a register exchange inside the warp (or half warp).
                     const int wq = row >> 5;
-                    float* dq_part = scr_a;                              // [4 warps][HD]
+                    constexpr bool two_q = TWOQ;                         // DW = 16: two queries per warp
+                    const int part_row = two_q ? (wq * 2 + (lane >> 4)) : wq;
+                    float* dq_part = scr_a;                              // [4 or 8 partial rows][HD]
                     const int slot = row_valid ? kb % max(ring_rows, 1) : 0;
                     // Rows that are not valid (delta >= w2, K2 row before the buffer, query past the end) have
                     // P = dS = 0, hence exact zeros in U and G: they need no masking in the sums below.
@@ -789,23 +792,38 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                                     v[e + 1] = __uint_as_float(g[e + 1]) * (bf16_hi(xw[e >> 1]) + p.k2_bias);
                                 }
                             }
-                            const float tot = warp_transpose_reduce<CW>(v, lane) * mult;
-                            if (lane < CW) dq_part[wq * HD + c * CW + lane] = tot;
+                            if constexpr (!two_q) {
+                                const float tot = warp_transpose_reduce<CW>(v, lane) * mult;
+                                if (lane < CW) dq_part[part_row * HD + c * CW + lane] = tot;
+                            } else {
+#pragma unroll
+                                for (int hb = 0; hb < CW / 16; ++hb) {
+                                    float vv[16];
+#pragma unroll
+                                    for (int e = 0; e < 16; ++e) vv[e] = v[16 * hb + e];
+                                    const float tot = half_warp_transpose_reduce16(vv, lane) * mult;
+                                    dq_part[part_row * HD + c * CW + 16 * hb + (lane & 15)] = tot;
+                                }
+                            }
                         }
                         SA_PROF_ADD(51 + 4 * grp, t_p1);
                         SA_PROF_T0(t_p2);
-                        if (need_kv2 && row_valid) {
-                            // staged read-modify-write: all loads, then all adds, then all stores
-                            float acc_r[CW];
+                        // ring update, staged (all loads, then all adds, then all stores).  With two queries in
+                        // a warp, lanes (q, delta) and (q+1, delta+1) own the same K2 row: the halves take turns.
+                        for (int turn = 0; turn < (two_q ? 2 : 1); ++turn) {
+                            if (need_kv2 && row_valid && (!two_q || (lane >> 4) == turn)) {
+                                float acc_r[CW];
 #pragma unroll
-                            for (int e = 0; e < CW; ++e) acc_r[e] = ring[ring_index<HD>(slot, c * CW + e)];
+                                for (int e = 0; e < CW; ++e) acc_r[e] = ring[ring_index<HD>(slot, c * CW + e)];
 #pragma unroll
-                            for (int e = 0; e < CW; e += 2) {
-                                acc_r[e] = fmaf(__uint_as_float(g[e]) * mult, bf16_lo(yw[e >> 1]), acc_r[e]);
-                                acc_r[e + 1] = fmaf(__uint_as_float(g[e + 1]) * mult, bf16_hi(yw[e >> 1]), acc_r[e + 1]);
+                                for (int e = 0; e < CW; e += 2) {
+                                    acc_r[e] = fmaf(__uint_as_float(g[e]) * mult, bf16_lo(yw[e >> 1]), acc_r[e]);
+                                    acc_r[e + 1] = fmaf(__uint_as_float(g[e + 1]) * mult, bf16_hi(yw[e >> 1]), acc_r[e + 1]);
+                                }
+#pragma unroll
+                                for (int e = 0; e < CW; ++e) ring[ring_index<HD>(slot, c * CW + e)] = acc_r[e];
                             }
-#pragma unroll
-                            for (int e = 0; e < CW; ++e) ring[ring_index<HD>(slot, c * CW + e)] = acc_r[e];
+                            if (two_q) __syncwarp();
                         }
                         SA_PROF_ADD(52 + 4 * grp, t_p2);
                         SA_PROF_T0(t_p3);
@@ -813,12 +831,12 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         SA_PROF_ADD(53 + 4 * grp, t_p3);
                     }
                     if (grp == 0 && dq != nullptr) {
-                        // warps per query = DW / 32; thread t finishes column t of every query of the tile
-                        const int wpq = DW >> 5;
+                        // partial rows per query: DW / 32 warps, or one half warp; thread t finishes column t
+                        const int ppq = two_q ? 1 : (DW >> 5);
                         if (row < HD) {
                             for (int q2 = 0; q2 < qpt; ++q2) {
                                 float a = 0.f;
-                                for (int w2i = 0; w2i < wpq; ++w2i) a += dq_part[(q2 * wpq + w2i) * HD + row];
+                                for (int w2i = 0; w2i < ppq; ++w2i) a += dq_part[(q2 * ppq + w2i) * HD + row];
                                 if (i0 + q2 < p.N)
                                     dq[ri.b * p.dq.b + (long)(i0 + q2) * p.dq.n + ri.h * p.dq.h + row] = __float2bfloat16_rn(a);
                             }
@@ -933,10 +951,10 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     for (int t = 0; t <= ru.nt; ++t) {
                         if (t < ru.nt) {
                             const uint32_t g = g_base + t;
-                            const int stage = (int)(g % kRowStages), b = t & 1;
+                            const int stage = (int)(g % NS), b = t & 1;
                             const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
                             const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
-                            mbar_wait(&B.st_full[stage], (g / kRowStages) & 1, wctx, 33);
+                            mbar_wait(&B.st_full[stage], (g / NS) & 1, wctx, 33);
                             tc_fence_after();
                             SA_PROF_T0(t_i1);
                             issue_sdp<HD>(tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false));
@@ -946,7 +964,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         if (t >= 1) {
                             const int tp = t - 1;
                             const uint32_t g = g_base + tp;
-                            const int stage = (int)(g % kRowStages), b = tp & 1;
+                            const int stage = (int)(g % NS), b = tp & 1;
                             const int width = (tp == ru.nt - 1) ? ru.last_width : kStreamRows;
                             const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
                             mbar_wait(&B.pds_ready[b], nb[b] & 1, wctx, 34);
@@ -978,11 +996,11 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 for (int i0 = ri.i_run0; i0 < ri.i_run1; i0 += qpt) {
                     const RowUnit ru = row_unit(P, i0);
                     for (int t = 0; t < ru.nt; ++t, ++g) {
-                        const int stage = (int)(g % kRowStages);
+                        const int stage = (int)(g % NS);
                         const int r0 = ru.col_start + t * kStreamRows;
                         uint8_t* k1_t = smem + L::kStream + stage * 2 * L::kSmallTile;
                         uint8_t* v1_t = k1_t + L::kSmallTile;
-                        mbar_wait(&B.st_empty[stage], ((g / kRowStages) & 1) ^ 1, wctx, 35);
+                        mbar_wait(&B.st_empty[stage], ((g / NS) & 1) ^ 1, wctx, 35);
                         mbar_arrive_expect_tx(&B.st_full[stage], 2 * L::kSmallTile);
 #pragma unroll
                         for (int sl = 0; sl < L::kSlabs; ++sl) {
@@ -1140,29 +1158,40 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         if (!make_map(&m2, v1, k.B, k.n1, k.Hkv, k.D, k.v1, kStreamRows)) return SA_ERR_BAD_STRIDE;
         const long grid = P.num_row_items < sm_count ? P.num_row_items : sm_count;
         const int need_kv2 = (dk2 || dv2) ? 1 : 0;
-        // shared-memory ring of fp32 dK2/dV2 rows if it fits beside the tiles
-        int ring_rows = (1 << pl.dw_log2) + pl.qpt;
+        // shared-memory ring of fp32 dK2/dV2 rows beside the tiles: with the 3-stage K1/V1 ring if it fits,
+        // else with 2 stages, else none (partials then accumulate in the workspace)
+        const int ring_want = (1 << pl.dw_log2) + pl.qpt;
+        auto launch_row = [&](auto kern, int k_ring, int k_min, int max_dyn, int hd) -> bool {
+            int ring_rows = ring_want;
+            int smem = k_ring + 1024 + 2 * ring_rows * hd * 4;
+            if (!need_kv2 || smem > max_dyn) { ring_rows = 0; smem = k_ring + 1024; }
+            if (smem < k_min) smem = k_min;
+            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn) != cudaSuccess) return false;
+            kern<<<(unsigned)grid, kRowThreads, smem, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o), (__nv_bfloat16*)dq,
+                                                            need_kv2, ring_rows);
+            return true;
+        };
+        bool ok;
         if (k.D == 128) {
-            using L = BwdSmem<128, kRowStages>;
-            int smem = L::kTotal + 1024 + 2 * ring_rows * 128 * 4;
-            if (!need_kv2 || smem > L::kMaxDynamic) { ring_rows = 0; smem = L::kAlloc; }
-            if (smem < L::kAlloc) smem = L::kAlloc;
-            auto kern = bwd_row_kernel<128>;
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kMaxDynamic) != cudaSuccess)
-                return SA_ERR_LAUNCH;
-            kern<<<(unsigned)grid, kRowThreads, smem, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o), (__nv_bfloat16*)dq,
-                                                            need_kv2, ring_rows);
+            using L3 = BwdSmem<128, 3>;
+            using L2 = BwdSmem<128, 2>;
+            const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 128 * 4 <= L3::kMaxDynamic;
+            if (pl.dw_log2 == 4)
+                ok = launch_row(bwd_row_kernel<128, 3, true>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128);
+            else
+                ok = (fits3 || !need_kv2) ? launch_row(bwd_row_kernel<128, 3, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128)
+                                          : launch_row(bwd_row_kernel<128, 2, false>, L2::kRing, L2::kAlloc, L2::kMaxDynamic, 128);
         } else {
-            using L = BwdSmem<64, kRowStages>;
-            int smem = L::kTotal + 1024 + 2 * ring_rows * 64 * 4;
-            if (!need_kv2 || smem > L::kMaxDynamic) { ring_rows = 0; smem = L::kAlloc; }
-            if (smem < L::kAlloc) smem = L::kAlloc;
-            auto kern = bwd_row_kernel<64>;
-            if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kMaxDynamic) != cudaSuccess)
-                return SA_ERR_LAUNCH;
-            kern<<<(unsigned)grid, kRowThreads, smem, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o), (__nv_bfloat16*)dq,
-                                                            need_kv2, ring_rows);
+            using L3 = BwdSmem<64, 3>;
+            using L2 = BwdSmem<64, 2>;
+            const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 64 * 4 <= L3::kMaxDynamic;
+            if (pl.dw_log2 == 4)
+                ok = launch_row(bwd_row_kernel<64, 3, true>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64);
+            else
+                ok = (fits3 || !need_kv2) ? launch_row(bwd_row_kernel<64, 3, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64)
+                                          : launch_row(bwd_row_kernel<64, 2, false>, L2::kRing, L2::kAlloc, L2::kMaxDynamic, 64);
         }
+        if (!ok) return SA_ERR_LAUNCH;
         ++*nlaunch;
         if (need_kv2) {
             const long total = (long)k.B * k.n2 * k.Hkv * (k.D / 2);

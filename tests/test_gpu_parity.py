@@ -86,6 +86,8 @@ ORACLE_CASES = [
     (1, 96, 2, 1, 128, 48, 12, 0.0, 0.0, 47, 11),      # a sequence shard with halo rows
     (1, 520, 1, 1, 64, 24, 1, 0.0, 0.0, 0, 0),         # w2 = 1: 128 queries per row tile
     (1, 130, 2, 2, 128, 300, 128, 0.0, 0.0, 0, 0),     # widest K2 window: one query per row tile
+    (1, 210, 2, 1, 64, 70, 14, 0.05, 0.0, 0, 0),       # D = 64 with 16 delta slots, two of them masked
+    (1, 300, 2, 2, 64, 90, 50, 0.0, 0.1, 0, 0),        # D = 64 with 64 delta slots
 ]
 
 
