@@ -72,9 +72,20 @@ __device__ unsigned long long g_prof_count[64];
             atomicAdd(&sa::ptx::g_prof_count[(site) & 63], 1ull);                          \
         }                                                                                  \
     } while (0)
+// Lifetime of a block in cycles: site 62 = block 0, site 63 = the longest-lived block.
+#define SA_PROF_LIFE(t0)                                                                   \
+    do {                                                                                   \
+        if (threadIdx.x == 0) {                                                            \
+            const unsigned long long dt_ = (unsigned long long)(clock64() - (t0));         \
+            if (blockIdx.x == 0) { sa::ptx::g_prof_cycles[62] = dt_; sa::ptx::g_prof_count[62] = 1; } \
+            atomicMax(&sa::ptx::g_prof_cycles[63], dt_);                                   \
+            sa::ptx::g_prof_count[63] = 1;                                                 \
+        }                                                                                  \
+    } while (0)
 #else
 #define SA_PROF_T0(name) do { } while (0)
 #define SA_PROF_ADD(site, t0) do { } while (0)
+#define SA_PROF_LIFE(t0) do { } while (0)
 #endif
 
 constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait in these kernels
@@ -174,6 +185,15 @@ __device__ __forceinline__ void tc_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                  : "memory");
 }
+// The same, issued by the elected lane of a convergent warp only.
+__device__ __forceinline__ void tc_commit(uint32_t leader, uint64_t* bar) {
+    asm volatile(
+        "{\n\t.reg .pred q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
+        ::"r"(smem_u32(bar)), "r"(leader)
+        : "memory");
+}
 
 // Each lane of the warp reads 16 (32) consecutive 32-bit columns of its own tensor-memory lane
 // (lane = 32 * (warp % 4) + laneid, encoded in bits 16.. of `addr`).
@@ -255,22 +275,37 @@ __host__ __device__ __forceinline__ uint32_t make_idesc(int m, int n, bool a_mn_
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+// The MMA-issuing warp runs its whole loop convergently (all 32 lanes wait on the barriers and
+// compute the descriptors, which the compiler can then keep in uniform registers) and only the
+// tcgen05 instructions themselves are predicated on one elected lane.  A loop executed by a single
+// lane inside a divergent branch issues one MMA every ~90 cycles when other warps are busy; the
+// convergent form sustains the tensor pipe's 64 cycles per 128x128x16 MMA.
+__device__ __forceinline__ uint32_t elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred;
+}
+
+// D[tmem] (+)= A[smem] * B[smem]       (issued by the lane whose `leader` is non-zero)
+__device__ __forceinline__ void mma_ss(uint32_t leader, uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       bool accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate), "r"(leader)
         : "memory");
 }
 // D[tmem] (+)= A[tmem] * B[smem]     (A: 128 lanes x K/2 columns, two bf16 per column)
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+__device__ __forceinline__ void mma_ts(uint32_t leader, uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                       bool accumulate) {
     asm volatile(
-        "{\n\t.reg .pred p;\n\t"
+        "{\n\t.reg .pred p, q;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        "setp.ne.b32 q, %5, 0;\n\t"
+        "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate), "r"(leader)
         : "memory");
 }
 
@@ -383,6 +418,7 @@ __device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab
     const int c = t % C, pr = t / C;
     const int kb_first = i0 + halo2 - (DW - 1);
     uint4 xa[NQ], ya[PASSES];
+    SA_PROF_T0(t_ld);
 #pragma unroll
     for (int q2 = 0; q2 < NQ; ++q2) {
         xa[q2] = make_uint4(0, 0, 0, 0);
@@ -395,6 +431,14 @@ __device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab
         ya[k] = make_uint4(0, 0, 0, 0);
         if (w < NWIN && kb >= 0) ya[k] = __ldg((const uint4*)(y + (int64_t)kb * ys) + c);
     }
+#ifdef SA_PROFILE
+#pragma unroll
+    for (int k = 0; k < PASSES; ++k) asm volatile("" ::"r"(ya[k].x), "r"(ya[k].w));
+#pragma unroll
+    for (int q2 = 0; q2 < NQ; ++q2) asm volatile("" ::"r"(xa[q2].x), "r"(xa[q2].w));
+    SA_PROF_ADD(60, t_ld);
+    SA_PROF_T0(t_st);
+#endif
 #pragma unroll
     for (int k = 0; k < PASSES; ++k) {
         const int w = pr + k * RPP;
@@ -410,6 +454,9 @@ __device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab
             *(uint4*)(tile + (c >> 3) * slab_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = out;
         }
     }
+#ifdef SA_PROFILE
+    SA_PROF_ADD(61, t_st);
+#endif
 }
 
 // Sum over the 32 lanes of a warp of CW values per lane; afterwards lane L holds the total of

@@ -193,23 +193,23 @@ __device__ __forceinline__ BwdBars bwd_bars(uint64_t* b) {
 // constants (a descriptor's low bits hold the address in 16-byte units, and no operand here ends
 // beyond 256 KiB, so adding to the 64-bit value never carries out of the address field).
 template <int HD>
-__device__ __forceinline__ void issue_sdp(uint32_t tm_s, uint32_t tm_dp, uint32_t x, uint32_t y, uint32_t w, uint32_t z,
+__device__ __forceinline__ void issue_sdp(uint32_t leader, uint32_t tm_s, uint32_t tm_dp, uint32_t x, uint32_t y, uint32_t w, uint32_t z,
                                           uint32_t idesc) {
     using L = BwdSmem<HD>;
     const uint64_t dx = ptx::desc_kmajor(x, 0), dy = ptx::desc_kmajor(y, 0);
     const uint64_t dw = ptx::desc_kmajor(w, 0), dz = ptx::desc_kmajor(z, 0);
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk)
-        ptx::mma_ss(tm_s, dx + (((kk >> 2) * L::kBigSlab + (kk & 3) * 32) >> 4),
+        ptx::mma_ss(leader, tm_s, dx + (((kk >> 2) * L::kBigSlab + (kk & 3) * 32) >> 4),
                     dw + (((kk >> 2) * L::kSmallSlab + (kk & 3) * 32) >> 4), idesc, kk > 0);
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk)
-        ptx::mma_ss(tm_dp, dy + (((kk >> 2) * L::kBigSlab + (kk & 3) * 32) >> 4),
+        ptx::mma_ss(leader, tm_dp, dy + (((kk >> 2) * L::kBigSlab + (kk & 3) * 32) >> 4),
                     dz + (((kk >> 2) * L::kSmallSlab + (kk & 3) * 32) >> 4), idesc, kk > 0);
 }
 
 template <int HD>
-__device__ __forceinline__ void issue_acc(uint32_t tm_acc1, uint32_t tm_acc2, uint32_t tm_p, uint32_t tm_ds, uint32_t w,
+__device__ __forceinline__ void issue_acc(uint32_t leader, uint32_t tm_acc1, uint32_t tm_acc2, uint32_t tm_p, uint32_t tm_ds, uint32_t w,
                                           uint32_t z, int ksteps, bool accumulate) {
     using L = BwdSmem<HD>;
     const uint32_t idesc = ptx::make_idesc(128, HD, false, true);
@@ -217,15 +217,15 @@ __device__ __forceinline__ void issue_acc(uint32_t tm_acc1, uint32_t tm_acc2, ui
     if (ksteps == kStreamRows / 16) {
 #pragma unroll
         for (int kk = 0; kk < kStreamRows / 16; ++kk)
-            ptx::mma_ts(tm_acc1, tm_p + kk * 8, dz + kk * (2048 >> 4), idesc, accumulate || kk > 0);
+            ptx::mma_ts(leader, tm_acc1, tm_p + kk * 8, dz + kk * (2048 >> 4), idesc, accumulate || kk > 0);
 #pragma unroll
         for (int kk = 0; kk < kStreamRows / 16; ++kk)
-            ptx::mma_ts(tm_acc2, tm_ds + kk * 8, dw + kk * (2048 >> 4), idesc, accumulate || kk > 0);
+            ptx::mma_ts(leader, tm_acc2, tm_ds + kk * 8, dw + kk * (2048 >> 4), idesc, accumulate || kk > 0);
     } else {
         for (int kk = 0; kk < ksteps; ++kk)
-            ptx::mma_ts(tm_acc1, tm_p + kk * 8, dz + kk * (2048 >> 4), idesc, accumulate || kk > 0);
+            ptx::mma_ts(leader, tm_acc1, tm_p + kk * 8, dz + kk * (2048 >> 4), idesc, accumulate || kk > 0);
         for (int kk = 0; kk < ksteps; ++kk)
-            ptx::mma_ts(tm_acc2, tm_ds + kk * 8, dw + kk * (2048 >> 4), idesc, accumulate || kk > 0);
+            ptx::mma_ts(leader, tm_acc2, tm_ds + kk * 8, dw + kk * (2048 >> 4), idesc, accumulate || kk > 0);
     }
 }
 
@@ -278,6 +278,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     const WaitCtx wctx{abort_flag, P.status};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    SA_PROF_T0(t_life);
     if (tid == 0) {
         for (int s = 0; s < kColStages; ++s) {
             mbar_init(&st_full[s], 256);
@@ -323,6 +324,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const int iq0 = (int)(rho0 >> P.dw_log2);
                 mbar_wait(sdp_ready, g & 1, wctx, 20);
                 tc_fence_after();
+                SA_PROF_T0(t_csm);
                 if (P.dw_log2 >= 4) {
                     // 16 columns (virtual rows) at a time, each chunk within one query; the next chunk's
                     // tensor-memory loads are in flight while the current one is processed
@@ -375,6 +377,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(pds_ready);
+                SA_PROF_ADD(28, t_csm);
             }
             g_base += nt;
             // epilogue: group 0 writes dV1, group 1 writes dK1 (times scale)
@@ -428,6 +431,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kColTileRows;
                 uint8_t* tile = smem + L::kStream + (stage * 2 + grp) * L::kTile;
                 mbar_wait(&st_empty[stage], ((g / kColStages) & 1) ^ 1, wctx, 22);
+                SA_PROF_T0(t_cform);
                 const __nv_bfloat16* xb = grp == 0 ? q + ci.b * p.q.b + h * p.q.h : d_o + ci.b * p.d_o.b + h * p.d_o.h;
                 const int64_t xs = grp == 0 ? p.q.n : p.d_o.n;
                 const __nv_bfloat16* yb = grp == 0 ? k2 + ci.b * p.k2.b + ci.hk * p.k2.h : v2 + ci.b * p.v2.b + ci.hk * p.v2.h;
@@ -455,6 +459,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(&st_full[stage]);
+                SA_PROF_ADD(37 + grp, t_cform);
             };
             for (int t = 0; t < nt; ++t) form_tile(t);
             g_base += nt;
@@ -462,7 +467,8 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     } else if (warp == 16) {
         // ---------------------------------------------------------------- MMA issuer
         reg_dealloc<80>();
-        if (lane == 0) {
+        {
+            const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
             uint32_t g_base = 0, n_items = 0;
             const uint32_t idesc_sd = make_idesc(128, kColTileRows, false, false);
             const uint32_t idesc_acc = make_idesc(128, HD, false, true);
@@ -483,30 +489,34 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     mbar_wait(&st_full[stage], (g / kColStages) & 1, wctx, 25);
                     tc_fence_after();
                     // S^T = K1 A^T,  dP^T = V1 C^T
+                    SA_PROF_T0(t_ci1);
 #pragma unroll
                     for (int kk = 0; kk < HD / 16; ++kk) {
                         const uint32_t off = ((kk >> 2) * L::kSlab + (kk & 3) * 32) >> 4;
-                        mma_ss(tm_s, d_k1 + off, d_a + off, idesc_sd, kk > 0);
+                        mma_ss(leader, tm_s, d_k1 + off, d_a + off, idesc_sd, kk > 0);
                     }
 #pragma unroll
                     for (int kk = 0; kk < HD / 16; ++kk) {
                         const uint32_t off = ((kk >> 2) * L::kSlab + (kk & 3) * 32) >> 4;
-                        mma_ss(tm_dp, d_v1 + off, d_c + off, idesc_sd, kk > 0);
+                        mma_ss(leader, tm_dp, d_v1 + off, d_c + off, idesc_sd, kk > 0);
                     }
-                    tc_commit(sdp_ready);
+                    tc_commit(leader, sdp_ready);
+                    SA_PROF_ADD(29, t_ci1);
                     mbar_wait(pds_ready, g & 1, wctx, 26);
                     tc_fence_after();
+                    SA_PROF_T0(t_ci2);
                     // dV1 += P^T-tile C-tile,  dK1 += dS^T-tile A-tile   (K = 128 virtual rows: 8 steps of 16)
 #pragma unroll
                     for (int kk = 0; kk < kColTileRows / 16; ++kk)
-                        mma_ts(tm_dv1, tm_s + (kk >> 2) * 64 + (kk & 3) * 8, d_cm + kk * (2048 >> 4), idesc_acc, t > 0 || kk > 0);
+                        mma_ts(leader, tm_dv1, tm_s + (kk >> 2) * 64 + (kk & 3) * 8, d_cm + kk * (2048 >> 4), idesc_acc, t > 0 || kk > 0);
 #pragma unroll
                     for (int kk = 0; kk < kColTileRows / 16; ++kk)
-                        mma_ts(tm_dk1, tm_dp + (kk >> 2) * 64 + (kk & 3) * 8, d_am + kk * (2048 >> 4), idesc_acc, t > 0 || kk > 0);
-                    tc_commit(&st_empty[stage]);
+                        mma_ts(leader, tm_dk1, tm_dp + (kk >> 2) * 64 + (kk & 3) * 8, d_am + kk * (2048 >> 4), idesc_acc, t > 0 || kk > 0);
+                    tc_commit(leader, &st_empty[stage]);
+                    SA_PROF_ADD(36, t_ci2);
                 }
-                tc_commit(acc_ready);
-                tc_commit(stat_empty);
+                tc_commit(leader, acc_ready);
+                tc_commit(leader, stat_empty);
                 g_base += nt;
                 ++n_items;
             }
@@ -538,6 +548,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     }
     tc_fence_before();
     __syncthreads();
+    SA_PROF_LIFE(t_life);
     if (warp == 16) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
@@ -636,6 +647,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     const WaitCtx wctx{abort_flag, P.status};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    SA_PROF_T0(t_life);
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&B.st_full[s], 1);
@@ -724,6 +736,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= kStreamRows - 1);
                     mbar_wait(&B.sdp_ready[grp], n_mine & 1, wctx, 30);
                     tc_fence_after();
+                    SA_PROF_T0(t_rsm);
 #pragma unroll 1
                     for (int c0 = 0; c0 < width; c0 += 32) {
                         uint32_t s[32], dp[32], pp[16], ds[16];
@@ -738,6 +751,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     tmem_wait_st();
                     tc_fence_before();
                     mbar_arrive(&B.pds_ready[grp]);
+                    SA_PROF_ADD(58 + grp, t_rsm);
                 }
                 // ---- epilogue: group 0 takes G (dQ and dK2 partials), group 1 takes U (dV2 partials)
                 const uint32_t acc = (grp == 0 ? tm_g : tm_u) + lane_addr;
@@ -937,7 +951,8 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     } else if (warp == 8) {
         // ---------------------------------------------------------------- MMA issuer
         reg_dealloc<72>();
-        if (lane == 0) {
+        {
+            const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
             uint32_t nb[2] = {0, 0}, g_base = 0, n_units = 0;
             const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false);
             const uint32_t a_s = smem_base + L::kStat0, c_s = smem_base + L::kStat1;
@@ -957,8 +972,8 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             mbar_wait(&B.st_full[stage], (g / NS) & 1, wctx, 33);
                             tc_fence_after();
                             SA_PROF_T0(t_i1);
-                            issue_sdp<HD>(tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false));
-                            tc_commit(&B.sdp_ready[b]);
+                            issue_sdp<HD>(leader, tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false));
+                            tc_commit(leader, &B.sdp_ready[b]);
                             SA_PROF_ADD(47, t_i1);
                         }
                         if (t >= 1) {
@@ -972,12 +987,12 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             tc_fence_after();
                             // U += P V1-tile ; G += dS K1-tile
                             SA_PROF_T0(t_i2);
-                            issue_acc<HD>(tm_u, tm_g, tm_s[b], tm_dp[b], k1_t, v1_t, width / 16, tp > 0);
-                            tc_commit(&B.st_empty[stage]);
+                            issue_acc<HD>(leader, tm_u, tm_g, tm_s[b], tm_dp[b], k1_t, v1_t, width / 16, tp > 0);
+                            tc_commit(leader, &B.st_empty[stage]);
                             SA_PROF_ADD(48, t_i2);
                         }
                     }
-                    tc_commit(B.acc_ready);
+                    tc_commit(leader, B.acc_ready);
                     SA_PROF_ADD(46, t_mma);
                     g_base += ru.nt;
                 }
@@ -1017,6 +1032,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     }
     tc_fence_before();
     __syncthreads();
+    SA_PROF_LIFE(t_life);
     if (warp == 8) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);

@@ -112,6 +112,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
     const WaitCtx wctx{abort_flag, P.status};
 
     const int tid = threadIdx.x;
+    SA_PROF_T0(t_life);
     const int warp = tid >> 5;
     const int lane = tid & 31;
 
@@ -177,7 +178,8 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
     } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         reg_dealloc<72>();
-        if (lane == 0) {
+        {
+            const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
             const uint32_t idesc_pv = make_idesc(128, HD, false, true);
             const uint32_t idesc_s_full = make_idesc(128, kColTile, false, false);
             uint32_t g = 0;          // ring position of the unit's first tile
@@ -194,9 +196,9 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
 #pragma unroll
                     for (int kk = 0; kk < HD / 16; ++kk) {
                         const uint32_t off = ((kk >> 2) * L::kSlabBytes + (kk & 3) * 32) >> 4;
-                        mma_ss(tmem_s[r], da + off, db + off, idesc_s, kk > 0);
+                        mma_ss(leader, tmem_s[r], da + off, db + off, idesc_s, kk > 0);
                     }
-                    tc_commit(&s_ready[r]);
+                    tc_commit(leader, &s_ready[r]);
                 };
                 auto issue_pv = [&](int r, int t) {
                     const int s = (g + t) % kStages;
@@ -204,11 +206,11 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                     if (t != ug.ntiles - 1) {
 #pragma unroll
                         for (int kk = 0; kk < kColTile / 16; ++kk)
-                            mma_ts(tmem_t[r], tmem_s[r] + kk * 8, db + kk * (2048 >> 4), idesc_pv, t > 0 || kk > 0);
+                            mma_ts(leader, tmem_t[r], tmem_s[r] + kk * 8, db + kk * (2048 >> 4), idesc_pv, t > 0 || kk > 0);
                     } else {
                         const int ksteps = ug.last_width / 16;
                         for (int kk = 0; kk < ksteps; ++kk)
-                            mma_ts(tmem_t[r], tmem_s[r] + kk * 8, db + kk * (2048 >> 4), idesc_pv, t > 0 || kk > 0);
+                            mma_ts(leader, tmem_t[r], tmem_s[r] + kk * 8, db + kk * (2048 >> 4), idesc_pv, t > 0 || kk > 0);
                     }
                 };
                 // prologue: S(0) of both row tiles
@@ -218,7 +220,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                     tc_fence_after();
                     issue_s(r, 0);
                 }
-                tc_commit(&k1_empty[g % kStages]);
+                tc_commit(leader, &k1_empty[g % kStages]);
                 for (int t = 0; t < ug.ntiles; ++t) {
                     const uint32_t gt = g + t;
                     for (int r = 0; r < kNumRowTiles; ++r) {
@@ -226,17 +228,21 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                         ++ns[r];
                         if (r == 0) mbar_wait(&v1_full[gt % kStages], (gt / kStages) & 1, wctx, 6);
                         tc_fence_after();
+                        SA_PROF_T0(t_pv);
                         issue_pv(r, t);
-                        if (r == kNumRowTiles - 1) tc_commit(&v1_empty[gt % kStages]);
+                        SA_PROF_ADD(30, t_pv);
+                        if (r == kNumRowTiles - 1) tc_commit(leader, &v1_empty[gt % kStages]);
                         if (t + 1 < ug.ntiles) {
                             if (r == 0) {
                                 mbar_wait(&k1_full[(gt + 1) % kStages], ((gt + 1) / kStages) & 1, wctx, 7);
                                 tc_fence_after();
                             }
+                            SA_PROF_T0(t_s);
                             issue_s(r, t + 1);
-                            if (r == kNumRowTiles - 1) tc_commit(&k1_empty[(gt + 1) % kStages]);
+                            SA_PROF_ADD(31, t_s);
+                            if (r == kNumRowTiles - 1) tc_commit(leader, &k1_empty[(gt + 1) % kStages]);
                         } else {
-                            tc_commit(&o_ready[r]);
+                            tc_commit(leader, &o_ready[r]);
                         }
                     }
                 }
@@ -329,6 +335,8 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                             for (int x = 0; x < 4; ++x) mx[x] = fmaxf(mx[x], __uint_as_float(v[cch & 1][e + x]));
                         }
                     }
+                    SA_PROF_ADD(20 + r, t_sm);
+                    SA_PROF_T0(t_p2);
                     tmem_ld32(s_addr, v[0]);                  // issued before the (rare) rescale so its latency overlaps
                     update_max(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c2);
                     float ls[2] = {0.f, 0.f};
@@ -349,6 +357,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                         tmem_st16(s_addr + 16 * cch, pk);
                     }
                     lsum = ls[0] + ls[1];
+                    SA_PROF_ADD(22 + r, t_p2);
                 } else {
                     // pass 1: row maximum of the valid columns
                     float tmax = -INFINITY;
@@ -382,11 +391,14 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                         }
                         tmem_st16(s_addr + (c0 >> 1), pk);
                     }
+                    SA_PROF_ADD((t == 0 ? 24 : 26) + r, t_sm);
                 }
                 l += lsum;
+                SA_PROF_T0(t_st);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&p_ready[r]);
+                SA_PROF_ADD(28 + r, t_st);
                 SA_PROF_ADD(16 + r, t_sm);
             }
             // ---- epilogue: merge the delta rows of each query
@@ -487,6 +499,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
     // ---------------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
+    SA_PROF_LIFE(t_life);
     if (warp == 9) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
