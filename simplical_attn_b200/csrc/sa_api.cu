@@ -166,14 +166,16 @@ int launch_fwd_tc(const sa_params* p, const KParams& k, const void* q, const voi
     const long grid = P.num_units < dev.sm_count ? P.num_units : dev.sm_count;
     if (k.D == 128) {
         using L = sa::tc::FwdSmem<128>;
-        auto kern = sa::tc::fwd_tc_kernel<128>;
+        const bool has_bias = k.k2_bias != 0.f || k.v2_bias != 0.f;
+        auto kern = has_bias ? sa::tc::fwd_tc_kernel<128, true> : sa::tc::fwd_tc_kernel<128, false>;
         if (!set_smem(kern, L::kAlloc)) return SA_ERR_LAUNCH;
         kern<<<(unsigned)grid, sa::tc::kFwdThreads, L::kAlloc, st>>>(P, map_k1, map_v1, (const __nv_bfloat16*)q,
                                                                       (const __nv_bfloat16*)k2, (const __nv_bfloat16*)v2,
                                                                       (__nv_bfloat16*)o, lse);
     } else {
         using L = sa::tc::FwdSmem<64>;
-        auto kern = sa::tc::fwd_tc_kernel<64>;
+        const bool has_bias = k.k2_bias != 0.f || k.v2_bias != 0.f;
+        auto kern = has_bias ? sa::tc::fwd_tc_kernel<64, true> : sa::tc::fwd_tc_kernel<64, false>;
         if (!set_smem(kern, L::kAlloc)) return SA_ERR_LAUNCH;
         kern<<<(unsigned)grid, sa::tc::kFwdThreads, L::kAlloc, st>>>(P, map_k1, map_v1, (const __nv_bfloat16*)q,
                                                                       (const __nv_bfloat16*)k2, (const __nv_bfloat16*)v2,

@@ -360,7 +360,8 @@ __device__ __forceinline__ uint4 mul_chunk_nobias(const uint4& xa, const uint4& 
     return make_uint4(hmul2_bf16(xa.x, ya.x), hmul2_bf16(xa.y, ya.y), hmul2_bf16(xa.z, ya.z), hmul2_bf16(xa.w, ya.w));
 }
 
-template <int HD, int NROWS, int NTHREADS, int MAXBATCH = 4>
+// BIAS = false: the bias is known to be zero (the common case) and the exact packed-bf16 product is used.
+template <int HD, int NROWS, int NTHREADS, bool BIAS, int MAXBATCH = 4>
 __device__ __forceinline__ void form_product_tile(uint8_t* tile, int slab_bytes, int t, long rho0, int dw_log2, int n_q,
                                                   int w2, int halo2, const __nv_bfloat16* x, int64_t xs,
                                                   const __nv_bfloat16* y, int64_t ys, float bias) {
@@ -392,7 +393,7 @@ __device__ __forceinline__ void form_product_tile(uint8_t* tile, int slab_bytes,
         for (int k = 0; k < BATCH; ++k) {
             const int r = t / C + (k0 + k) * RPP;
             uint4 out = make_uint4(0, 0, 0, 0);
-            if (ok[k]) out = (bias == 0.f) ? mul_chunk_nobias(xa[k], ya[k]) : mul_chunk(xa[k], ya[k], bias);
+            if (ok[k]) out = BIAS ? mul_chunk(xa[k], ya[k], bias) : mul_chunk_nobias(xa[k], ya[k]);
             *(uint4*)(tile + (c >> 3) * slab_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = out;
         }
     }
@@ -405,7 +406,7 @@ __device__ __forceinline__ void form_product_tile(uint8_t* tile, int slab_bytes,
 // used for all the queries it pairs with: consecutive queries share all but one of their DW rows.
 // Window row w (0 <= w < DW + nq - 1) is y row  kb = i0 + halo2 - (DW-1) + w ; it meets query x at
 // delta = DW - 1 + x - w.  One round of loads per tile: NQ chunks of x and PASSES chunks of y.
-template <int HD, int DWLOG, int NTHREADS = 128>
+template <int HD, int DWLOG, bool BIAS, int NTHREADS = 128>
 __device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab_bytes, int t, int i0, int n_q, int w2,
                                                          int halo2, const __nv_bfloat16* x, int64_t xs,
                                                          const __nv_bfloat16* y, int64_t ys, float bias) {
@@ -450,13 +451,28 @@ __device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab
             const int r = q2 * DW + dlt;
             uint4 out = make_uint4(0, 0, 0, 0);
             if (i0 + q2 < n_q && dlt < w2 && kb >= 0)
-                out = (bias == 0.f) ? mul_chunk_nobias(xa[q2], ya[k]) : mul_chunk(xa[q2], ya[k], bias);
+                out = BIAS ? mul_chunk(xa[q2], ya[k], bias) : mul_chunk_nobias(xa[q2], ya[k]);
             *(uint4*)(tile + (c >> 3) * slab_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = out;
         }
     }
 #ifdef SA_PROFILE
     SA_PROF_ADD(61, t_st);
 #endif
+}
+
+// A 128-row product tile that starts at query i0 (DW = 1 << dw_log2 delta slots per query): the
+// shared-window form for 16, 32 and 64 slots (one round of loads), the general form otherwise.
+template <int HD, bool BIAS>
+__device__ __forceinline__ void form_query_tile(uint8_t* tile, int slab_bytes, int t, int i0, int dw_log2, int n_q, int w2,
+                                                int halo2, const __nv_bfloat16* x, int64_t xs, const __nv_bfloat16* y,
+                                                int64_t ys, float bias) {
+    switch (dw_log2) {
+        case 4: form_product_tile_shared<HD, 4, BIAS>(tile, slab_bytes, t, i0, n_q, w2, halo2, x, xs, y, ys, bias); break;
+        case 5: form_product_tile_shared<HD, 5, BIAS>(tile, slab_bytes, t, i0, n_q, w2, halo2, x, xs, y, ys, bias); break;
+        case 6: form_product_tile_shared<HD, 6, BIAS>(tile, slab_bytes, t, i0, n_q, w2, halo2, x, xs, y, ys, bias); break;
+        default:
+            form_product_tile<HD, 128, 128, BIAS>(tile, slab_bytes, t, (long)i0 << dw_log2, dw_log2, n_q, w2, halo2, x, xs, y, ys, bias);
+    }
 }
 
 // Sum over the 32 lanes of a warp of CW values per lane; afterwards lane L holds the total of

@@ -252,7 +252,7 @@ struct ColSmem {
 // shared memory either way) and in long bursts.  S^T / dP^T are not double buffered (tensor memory
 // is full: 128 + 128 + 2 x 128 accumulator columns); instead both softmax groups work on the same
 // tile, group g on columns [64g, 64g + 64), and write P / dS back inside their own column range.
-template <int HD>
+template <int HD, bool BIAS>
 __global__ void __launch_bounds__(kColThreads, 1)
 bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
                const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
@@ -436,14 +436,14 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const int64_t xs = grp == 0 ? p.q.n : p.d_o.n;
                 const __nv_bfloat16* yb = grp == 0 ? k2 + ci.b * p.k2.b + ci.hk * p.k2.h : v2 + ci.b * p.v2.b + ci.hk * p.v2.h;
                 const int64_t ys = grp == 0 ? p.k2.n : p.v2.n;
-                const float bias = grp == 0 ? p.k2_bias : p.v2_bias;
+                const float bias = BIAS ? (grp == 0 ? p.k2_bias : p.v2_bias) : 0.f;
                 const int iq0 = (int)(rho0 >> P.dw_log2);
                 switch (P.dw_log2) {     // whole queries per tile: share the K2 / V2 rows between them
-                    case 4: form_product_tile_shared<HD, 4>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
-                    case 5: form_product_tile_shared<HD, 5>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
-                    case 6: form_product_tile_shared<HD, 6>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
+                    case 4: form_product_tile_shared<HD, 4, BIAS>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
+                    case 5: form_product_tile_shared<HD, 5, BIAS>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
+                    case 6: form_product_tile_shared<HD, 6, BIAS>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
                     default:
-                        form_product_tile<HD, kColTileRows, 128>(tile, L::kSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2, xb, xs,
+                        form_product_tile<HD, kColTileRows, 128, BIAS>(tile, L::kSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2, xb, xs,
                                                                  yb, ys, bias);
                 }
                 if (grp == 0) {
@@ -628,7 +628,7 @@ __device__ __forceinline__ int ring_index(int slot, int col) {
     return slot * HD + ((col & ~31) | ((col ^ slot) & 31));
 }
 
-template <int HD, int NS, bool TWOQ>
+template <int HD, int NS, bool TWOQ, bool BIAS>
 __global__ void __launch_bounds__(kRowThreads, 1)
 bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
                const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
@@ -712,13 +712,13 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 // ---- stationary operand of this group
                 SA_PROF_T0(t_form);
                 if (grp == 0)
-                    form_product_tile<HD, 128, 128>(my_tile, L::kBigSlab, row, (long)i0 << P.dw_log2, P.dw_log2, p.N, p.w2, p.halo2,
-                                          q + ri.b * p.q.b + ri.h * p.q.h, p.q.n, k2 + ri.b * p.k2.b + ri.hk * p.k2.h, p.k2.n,
-                                          p.k2_bias);
+                    form_query_tile<HD, BIAS>(my_tile, L::kBigSlab, row, i0, P.dw_log2, p.N, p.w2, p.halo2,
+                                              q + ri.b * p.q.b + ri.h * p.q.h, p.q.n, k2 + ri.b * p.k2.b + ri.hk * p.k2.h, p.k2.n,
+                                              BIAS ? p.k2_bias : 0.f);
                 else
-                    form_product_tile<HD, 128, 128>(my_tile, L::kBigSlab, row, (long)i0 << P.dw_log2, P.dw_log2, p.N, p.w2, p.halo2,
-                                          d_o + ri.b * p.d_o.b + ri.h * p.d_o.h, p.d_o.n,
-                                          v2 + ri.b * p.v2.b + ri.hk * p.v2.h, p.v2.n, p.v2_bias);
+                    form_query_tile<HD, BIAS>(my_tile, L::kBigSlab, row, i0, P.dw_log2, p.N, p.w2, p.halo2,
+                                              d_o + ri.b * p.d_o.b + ri.h * p.d_o.h, p.d_o.n,
+                                              v2 + ri.b * p.v2.b + ri.hk * p.v2.h, p.v2.n, BIAS ? p.v2_bias : 0.f);
                 fence_proxy_async_smem();
                 tc_fence_before();
                 mbar_arrive(B.stat_full);
@@ -793,7 +793,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         SA_PROF_T0(t_p1);
                         if (grp == 0 && dq != nullptr) {
                             float v[CW];
-                            if (p.k2_bias == 0.f) {
+                            if constexpr (!BIAS) {
 #pragma unroll
                                 for (int e = 0; e < CW; e += 2) {
                                     v[e] = __uint_as_float(g[e]) * bf16_lo(xw[e >> 1]);
@@ -870,7 +870,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         load_bf16_words<CW>(k2_row + c * CW, xw);
 #pragma unroll
                         for (int e = 0; e < CW; ++e) {
-                            const float xf = ((e & 1) ? bf16_hi(xw[e >> 1]) : bf16_lo(xw[e >> 1])) + p.k2_bias;
+                            const float xf = ((e & 1) ? bf16_hi(xw[e >> 1]) : bf16_lo(xw[e >> 1])) + (BIAS ? p.k2_bias : 0.f);
                             scr_a[row * CW + (e ^ (row & (CW - 1)))] = row_valid ? __uint_as_float(g[e]) * xf * mult : 0.f;
                         }
                     }
@@ -1146,20 +1146,21 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
     prep_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(k, bf(o), bf(d_o), lse, lse2, delta);
     ++*nlaunch;
 
+    const bool has_bias = k.k2_bias != 0.f || k.v2_bias != 0.f;     // selects the kernels that carry the bias adds
     if (dk1 || dv1) {
         CUtensorMap m1, m2;
         if (!make_map(&m1, k1, k.B, k.n1, k.Hkv, k.D, k.k1, 128)) return SA_ERR_BAD_STRIDE;
         if (!make_map(&m2, v1, k.B, k.n1, k.Hkv, k.D, k.v1, 128)) return SA_ERR_BAD_STRIDE;
         const long grid = P.num_col_items < sm_count ? P.num_col_items : sm_count;
         if (k.D == 128) {
-            auto kern = bwd_col_kernel<128>;
+            auto kern = has_bias ? bwd_col_kernel<128, true> : bwd_col_kernel<128, false>;
             using LC = ColSmem<128>;
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LC::kAlloc) != cudaSuccess)
                 return SA_ERR_LAUNCH;
             kern<<<(unsigned)grid, kColThreads, LC::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
                                                                              (__nv_bfloat16*)dk1, (__nv_bfloat16*)dv1);
         } else {
-            auto kern = bwd_col_kernel<64>;
+            auto kern = has_bias ? bwd_col_kernel<64, true> : bwd_col_kernel<64, false>;
             using LC = ColSmem<64>;
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LC::kAlloc) != cudaSuccess)
                 return SA_ERR_LAUNCH;
@@ -1193,19 +1194,19 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
             using L2 = BwdSmem<128, 2>;
             const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 128 * 4 <= L3::kMaxDynamic;
             if (pl.dw_log2 == 4)
-                ok = launch_row(bwd_row_kernel<128, 3, true>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128);
+                ok = launch_row(has_bias ? bwd_row_kernel<128, 3, true, true> : bwd_row_kernel<128, 3, true, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128);
             else
-                ok = (fits3 || !need_kv2) ? launch_row(bwd_row_kernel<128, 3, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128)
-                                          : launch_row(bwd_row_kernel<128, 2, false>, L2::kRing, L2::kAlloc, L2::kMaxDynamic, 128);
+                ok = (fits3 || !need_kv2) ? launch_row(has_bias ? bwd_row_kernel<128, 3, false, true> : bwd_row_kernel<128, 3, false, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128)
+                                          : launch_row(has_bias ? bwd_row_kernel<128, 2, false, true> : bwd_row_kernel<128, 2, false, false>, L2::kRing, L2::kAlloc, L2::kMaxDynamic, 128);
         } else {
             using L3 = BwdSmem<64, 3>;
             using L2 = BwdSmem<64, 2>;
             const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 64 * 4 <= L3::kMaxDynamic;
             if (pl.dw_log2 == 4)
-                ok = launch_row(bwd_row_kernel<64, 3, true>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64);
+                ok = launch_row(has_bias ? bwd_row_kernel<64, 3, true, true> : bwd_row_kernel<64, 3, true, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64);
             else
-                ok = (fits3 || !need_kv2) ? launch_row(bwd_row_kernel<64, 3, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64)
-                                          : launch_row(bwd_row_kernel<64, 2, false>, L2::kRing, L2::kAlloc, L2::kMaxDynamic, 64);
+                ok = (fits3 || !need_kv2) ? launch_row(has_bias ? bwd_row_kernel<64, 3, false, true> : bwd_row_kernel<64, 3, false, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64)
+                                          : launch_row(has_bias ? bwd_row_kernel<64, 2, false, true> : bwd_row_kernel<64, 2, false, false>, L2::kRing, L2::kAlloc, L2::kMaxDynamic, 64);
         }
         if (!ok) return SA_ERR_LAUNCH;
         ++*nlaunch;

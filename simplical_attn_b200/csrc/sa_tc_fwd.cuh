@@ -85,7 +85,8 @@ __device__ __forceinline__ UnitGeom unit_geom(const FwdTcParams& P, long u) {
     return g;
 }
 
-template <int HD>
+// BIAS = false: both biases are zero, every bias add folds away.
+template <int HD, bool BIAS>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
               const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
@@ -97,6 +98,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
     const KParams& p = P.k;
+    const float k2_bias = BIAS ? p.k2_bias : 0.f, v2_bias = BIAS ? p.v2_bias : 0.f;
 
     uint64_t* bars = (uint64_t*)(smem + L::kBars);
     uint64_t* k1_full = bars;                       // [kStages]
@@ -273,9 +275,8 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
             const bool row_valid = (i < p.N) && (delta < p.w2) && (kb >= 0);
             // ---- form A_r: row (i, delta) = Q_i * (K2_{i-delta} + bias) as bf16, 128-byte swizzled
             SA_PROF_T0(t_form);
-            form_product_tile<HD, kRowTile, kRowTile>(a_tile, L::kSlabBytes, row, (long)(ug.i0 + r * qpt) << P.dw_log2, P.dw_log2,
-                                  p.N, p.w2, p.halo2, q + ug.b * p.q.b + ug.h * p.q.h, p.q.n,
-                                  k2 + ug.b * p.k2.b + ug.hk * p.k2.h, p.k2.n, p.k2_bias);
+            form_query_tile<HD, BIAS>(a_tile, L::kSlabBytes, row, ug.i0 + r * qpt, P.dw_log2, p.N, p.w2, p.halo2,
+                                      q + ug.b * p.q.b + ug.h * p.q.h, p.q.n, k2 + ug.b * p.k2.b + ug.hk * p.k2.h, p.k2.n, k2_bias);
             fence_proxy_async_smem();
             mbar_arrive(&a_ready[r]);
             SA_PROF_ADD(10 + r, t_form);
@@ -404,15 +405,24 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
             // ---- epilogue: merge the delta rows of each query
             SA_PROF_ADD(12 + r, t_loop);
             SA_PROF_T0(t_epi);
-            m_s[row] = m;
-            l_s[row] = l;
-            named_barrier_sync(1 + r, kRowTile);
-            float mq = -INFINITY;
-            for (int d2 = 0; d2 < DW; ++d2) mq = fmaxf(mq, m_s[(qq << P.dw_log2) + d2]);
-            float lq = 0.f;
-            for (int d2 = 0; d2 < DW; ++d2) {
-                const float mm = m_s[(qq << P.dw_log2) + d2];
-                if (mm > -INFINITY) lq += ex2(mm - mq) * l_s[(qq << P.dw_log2) + d2];
+            float mq, lq;
+            if (P.dw_log2 <= 5) {
+                // the delta rows of a query are DW consecutive lanes of one warp: merge by register exchange
+                mq = m;
+                for (int sft = DW >> 1; sft >= 1; sft >>= 1) mq = fmaxf(mq, __shfl_xor_sync(0xffffffffu, mq, sft));
+                lq = (m > -INFINITY) ? ex2(m - mq) * l : 0.f;
+                for (int sft = DW >> 1; sft >= 1; sft >>= 1) lq += __shfl_xor_sync(0xffffffffu, lq, sft);
+            } else {
+                m_s[row] = m;
+                l_s[row] = l;
+                named_barrier_sync(1 + r, kRowTile);
+                mq = -INFINITY;
+                for (int d2 = 0; d2 < DW; ++d2) mq = fmaxf(mq, m_s[(qq << P.dw_log2) + d2]);
+                lq = 0.f;
+                for (int d2 = 0; d2 < DW; ++d2) {
+                    const float mm = m_s[(qq << P.dw_log2) + d2];
+                    if (mm > -INFINITY) lq += ex2(mm - mq) * l_s[(qq << P.dw_log2) + d2];
+                }
             }
             const float wrow = (m > -INFINITY) ? ex2(m - mq) / lq : 0.f;
             mbar_wait(&o_ready[r], nu & 1, wctx, 9);
@@ -438,8 +448,8 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                     float y[32];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
-                        y[e] = row_valid ? __uint_as_float(v[e]) * wrow * (bf16_lo(vw[e >> 1]) + p.v2_bias) : 0.f;
-                        y[e + 1] = row_valid ? __uint_as_float(v[e + 1]) * wrow * (bf16_hi(vw[e >> 1]) + p.v2_bias) : 0.f;
+                        y[e] = row_valid ? __uint_as_float(v[e]) * wrow * (bf16_lo(vw[e >> 1]) + v2_bias) : 0.f;
+                        y[e + 1] = row_valid ? __uint_as_float(v[e + 1]) * wrow * (bf16_hi(vw[e >> 1]) + v2_bias) : 0.f;
                     }
                     tot[cch] = warp_transpose_reduce<32>(y, lane);
                 }
@@ -474,7 +484,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
                     const float vf = (e & 1) ? bf16_hi(vw[e >> 1]) : bf16_lo(vw[e >> 1]);
-                    const float val = row_valid ? __uint_as_float(v[e]) * wrow * (vf + p.v2_bias) : 0.f;
+                    const float val = row_valid ? __uint_as_float(v[e]) * wrow * (vf + v2_bias) : 0.f;
                     scratch[row * 32 + (e ^ (row & 31))] = val;
                 }
                 named_barrier_sync(1 + r, kRowTile);
