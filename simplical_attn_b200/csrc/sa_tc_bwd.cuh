@@ -621,11 +621,12 @@ __device__ __forceinline__ void load_bf16_cw(const __nv_bfloat16* row, int col, 
 }
 
 
-// Index into a ring of fp32 rows [slot][HD]; the low five column bits are XOR-ed with the slot so
-// that a warp whose lanes hold the same column of 32 consecutive rows hits 32 different banks.
+// Index into a ring of fp32 rows [slot][HD + 1]: the odd row pitch puts the same column of 32
+// consecutive rows into 32 different banks, and a column offset known at compile time stays an
+// immediate in the address.
 template <int HD>
 __device__ __forceinline__ int ring_index(int slot, int col) {
-    return slot * HD + ((col & ~31) | ((col ^ slot) & 31));
+    return slot * (HD + 1) + col;
 }
 
 template <int HD, int NS, bool TWOQ, bool BIAS>
@@ -692,8 +693,8 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         float* scr_b = scr_a + 128 * CW;
         // fp32 accumulators of the dK2 (group 0) / dV2 (group 1) rows currently within reach of the
         // block's queries, one slot per row modulo ring_rows; ring_rows == 0: not enough shared memory
-        float* ring = (float*)(smem + L::kRing) + grp * ring_rows * HD;
-        for (int x = row; x < ring_rows * HD; x += 128) ring[x] = 0.f;
+        float* ring = (float*)(smem + L::kRing) + grp * ring_rows * (HD + 1);
+        for (int x = row; x < ring_rows * (HD + 1); x += 128) ring[x] = 0.f;
         named_barrier_sync(1 + grp, 128);
         int flush_lo = 0;
         uint32_t n_mine = 0, n_units = 0;
@@ -831,8 +832,8 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                                 for (int e = 0; e < CW; ++e) acc_r[e] = ring[ring_index<HD>(slot, c * CW + e)];
 #pragma unroll
                                 for (int e = 0; e < CW; e += 2) {
-                                    acc_r[e] = fmaf(__uint_as_float(g[e]) * mult, bf16_lo(yw[e >> 1]), acc_r[e]);
-                                    acc_r[e + 1] = fmaf(__uint_as_float(g[e + 1]) * mult, bf16_hi(yw[e >> 1]), acc_r[e + 1]);
+                                    acc_r[e] = fmaf(__uint_as_float(g[e]), bf16_lo(yw[e >> 1]), acc_r[e]);
+                                    acc_r[e + 1] = fmaf(__uint_as_float(g[e + 1]), bf16_hi(yw[e >> 1]), acc_r[e + 1]);
                                 }
 #pragma unroll
                                 for (int e = 0; e < CW; ++e) ring[ring_index<HD>(slot, c * CW + e)] = acc_r[e];
@@ -877,7 +878,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 #pragma unroll
                     for (int e = 0; e < CW; ++e) {
                         const float yf = (e & 1) ? bf16_hi(yw[e >> 1]) : bf16_lo(yw[e >> 1]);
-                        scr_b[row * CW + (e ^ (row & (CW - 1)))] = row_valid ? __uint_as_float(g[e]) * yf * mult : 0.f;
+                        scr_b[row * CW + (e ^ (row & (CW - 1)))] = row_valid ? __uint_as_float(g[e]) * yf : 0.f;
                     }
                     named_barrier_sync(1 + grp, 128);
                     if (grp == 0 && dq != nullptr) {
@@ -920,7 +921,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                                     dst = ws_head + ((bh * P.num_runs + ri.run) * (p.w2 - 1) + slot) * HD + c * CW + e;
                                     first = uidx == 0;
                                 }
-                                *dst = first ? a : *dst + a;
+                                *dst = first ? a * mult : fmaf(a, mult, *dst);
                             }
                         }
                     }
@@ -937,7 +938,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                                                    : ws_head + ((bh * P.num_runs + ri.run) * (p.w2 - 1) + (kbf - (own0 - (p.w2 - 1)))) * HD;
                         for (int d = row; d < HD; d += 128) {
                             float* src = ring + ring_index<HD>(slot, d);
-                            dst[d] = *src;
+                            dst[d] = *src * mult;          // the ring holds unscaled sums
                             *src = 0.f;
                         }
                     }
@@ -1180,7 +1181,7 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         const int ring_want = (1 << pl.dw_log2) + pl.qpt;
         auto launch_row = [&](auto kern, int k_ring, int k_min, int max_dyn, int hd) -> bool {
             int ring_rows = ring_want;
-            int smem = k_ring + 1024 + 2 * ring_rows * hd * 4;
+            int smem = k_ring + 1024 + 2 * ring_rows * (hd + 1) * 4;
             if (!need_kv2 || smem > max_dyn) { ring_rows = 0; smem = k_ring + 1024; }
             if (smem < k_min) smem = k_min;
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn) != cudaSuccess) return false;
@@ -1192,7 +1193,7 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         if (k.D == 128) {
             using L3 = BwdSmem<128, 3>;
             using L2 = BwdSmem<128, 2>;
-            const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 128 * 4 <= L3::kMaxDynamic;
+            const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 129 * 4 <= L3::kMaxDynamic;
             if (pl.dw_log2 == 4)
                 ok = launch_row(has_bias ? bwd_row_kernel<128, 3, true, true> : bwd_row_kernel<128, 3, true, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128);
             else
@@ -1201,7 +1202,7 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         } else {
             using L3 = BwdSmem<64, 3>;
             using L2 = BwdSmem<64, 2>;
-            const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 64 * 4 <= L3::kMaxDynamic;
+            const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 65 * 4 <= L3::kMaxDynamic;
             if (pl.dw_log2 == 4)
                 ok = launch_row(has_bias ? bwd_row_kernel<64, 3, true, true> : bwd_row_kernel<64, 3, true, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64);
             else

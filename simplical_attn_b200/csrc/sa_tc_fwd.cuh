@@ -295,7 +295,20 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                 SA_PROF_T0(t_sm);
                 const uint32_t s_addr = tmem_s[r] + lane_addr;
                 // a tile is "full" when every column is inside every row's window: no masks needed
-                const bool full = (width == kColTile) && __all_sync(0xffffffffu, lo <= 0 && hi >= kColTile - 1);
+                bool full = (width == kColTile) && __all_sync(0xffffffffu, lo <= 0 && hi >= kColTile - 1);
+                if (!full && width == kColTile && __all_sync(0xffffffffu, lo <= 16 && hi >= kColTile - 1)) {
+                    // The first tile of a unit: only the first few columns lie before the window of some rows.
+                    // Overwrite those scores with a large negative number (their P becomes exactly 0) and
+                    // treat the tile as full.
+                    uint32_t e16[16];
+                    tmem_ld16(s_addr, e16);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int e = 0; e < 16; ++e) e16[e] = (e < lo) ? __float_as_uint(-1e30f) : e16[e];
+                    tmem_st16(s_addr, e16);
+                    tmem_wait_st();
+                    full = true;
+                }
                 float lsum = 0.f;
                 // running maximum, lazily updated: returns the factor the row's T and l must be scaled by
                 auto update_max = [&](float tmax) {
@@ -425,11 +438,16 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                 }
             }
             const float wrow = (m > -INFINITY) ? ex2(m - mq) / lq : 0.f;
-            mbar_wait(&o_ready[r], nu & 1, wctx, 9);
-            tc_fence_after();
             const __nv_bfloat16* v2row = v2 + ug.b * p.v2.b + (long)max(kb, 0) * p.v2.n + ug.hk * p.v2.h;
             const uint32_t t_addr = tmem_t[r] + lane_addr;
             if (P.dw_log2 >= 5) {
+                // this row's V2 values, fetched while the last MMAs of the unit are still running
+                uint32_t vw[HD / 2];
+#pragma unroll
+                for (int e = 0; e < HD / 2; ++e) vw[e] = 0u;
+                if (row_valid) load_bf16_words<HD>(v2row, vw);
+                mbar_wait(&o_ready[r], nu & 1, wctx, 9);
+                tc_fence_after();
                 // a warp holds 32 consecutive deltas of one query: sum them by a register exchange;
                 // lane L ends up with column L of each 32-column chunk
                 const int wq = row >> 5;                      // warp within the group
@@ -440,16 +458,12 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                 for (int cch = 0; cch < HD / 32; ++cch) {
                     uint32_t v[32];
                     tmem_ld32(t_addr + 32 * cch, v);
-                    uint32_t vw[16];
-#pragma unroll
-                    for (int e = 0; e < 16; ++e) vw[e] = 0u;
-                    if (row_valid) load_bf16_words<32>(v2row + 32 * cch, vw);
                     tmem_wait_ld();
                     float y[32];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
-                        y[e] = row_valid ? __uint_as_float(v[e]) * wrow * (bf16_lo(vw[e >> 1]) + v2_bias) : 0.f;
-                        y[e + 1] = row_valid ? __uint_as_float(v[e + 1]) * wrow * (bf16_hi(vw[e >> 1]) + v2_bias) : 0.f;
+                        y[e] = row_valid ? __uint_as_float(v[e]) * wrow * (bf16_lo(vw[16 * cch + (e >> 1)]) + v2_bias) : 0.f;
+                        y[e + 1] = row_valid ? __uint_as_float(v[e + 1]) * wrow * (bf16_hi(vw[16 * cch + (e >> 1)]) + v2_bias) : 0.f;
                     }
                     tot[cch] = warp_transpose_reduce<32>(y, lane);
                 }
@@ -473,6 +487,8 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                     named_barrier_sync(1 + r, kRowTile);
                 }
             } else {
+            mbar_wait(&o_ready[r], nu & 1, wctx, 9);
+            tc_fence_after();
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 uint32_t v[32];
                 tmem_ld32(t_addr + c0, v);
