@@ -115,24 +115,25 @@ prep_kernel(KParams p, const __nv_bfloat16* __restrict__ o, const __nv_bfloat16*
 template <bool MASKED, int W = 32>
 __device__ __forceinline__ void softmax_bwd_chunk(const uint32_t (&s)[W], const uint32_t (&dp)[W], int c0, int lo, int hi,
                                                   float c2, float lse2, float delta, uint32_t (&pp)[W / 2], uint32_t (&ds)[W / 2]) {
+    // packed two-wide fp32 arithmetic (one instruction per pair of columns)
+    const float2 c2v = make_float2(c2, c2), nl = make_float2(-lse2, -lse2), nd = make_float2(-delta, -delta);
 #pragma unroll
     for (int e = 0; e < W; e += 2) {
-        float p0 = ptx::ex2(fmaf(__uint_as_float(s[e]), c2, -lse2));
-        float p1 = ptx::ex2(fmaf(__uint_as_float(s[e + 1]), c2, -lse2));
+        const float2 x = __ffma2_rn(make_float2(__uint_as_float(s[e]), __uint_as_float(s[e + 1])), c2v, nl);
+        float2 pr = make_float2(ptx::ex2(x.x), ptx::ex2(x.y));
         if (MASKED) {
             const int c = c0 + e;
-            p0 = (c >= lo && c <= hi) ? p0 : 0.f;
-            p1 = (c + 1 >= lo && c + 1 <= hi) ? p1 : 0.f;
+            pr.x = (c >= lo && c <= hi) ? pr.x : 0.f;
+            pr.y = (c + 1 >= lo && c + 1 <= hi) ? pr.y : 0.f;
         }
-        float d0 = p0 * (__uint_as_float(dp[e]) - delta);
-        float d1 = p1 * (__uint_as_float(dp[e + 1]) - delta);
+        float2 d = __fmul2_rn(pr, __fadd2_rn(make_float2(__uint_as_float(dp[e]), __uint_as_float(dp[e + 1])), nd));
         if (MASKED) {      // a masked column may hold stale tensor-memory contents (NaN): select, never multiply
             const int c = c0 + e;
-            d0 = (c >= lo && c <= hi) ? d0 : 0.f;
-            d1 = (c + 1 >= lo && c + 1 <= hi) ? d1 : 0.f;
+            d.x = (c >= lo && c <= hi) ? d.x : 0.f;
+            d.y = (c + 1 >= lo && c + 1 <= hi) ? d.y : 0.f;
         }
-        pp[e >> 1] = ptx::pack_bf16(p0, p1);
-        ds[e >> 1] = ptx::pack_bf16(d0, d1);
+        pp[e >> 1] = ptx::pack_bf16(pr.x, pr.y);
+        ds[e >> 1] = ptx::pack_bf16(d.x, d.y);
     }
 }
 

@@ -353,7 +353,9 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                     SA_PROF_T0(t_p2);
                     tmem_ld32(s_addr, v[0]);                  // issued before the (rare) rescale so its latency overlaps
                     update_max(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * c2);
-                    float ls[2] = {0.f, 0.f};
+                    // packed two-wide fp32 arithmetic: one FMA and one add per pair of columns
+                    float2 ls = make_float2(0.f, 0.f);
+                    const float2 c2v = make_float2(c2, c2), nm = make_float2(-m, -m);
 #pragma unroll
                     for (int cch = 0; cch < 4; ++cch) {
                         tmem_wait_ld();
@@ -361,16 +363,15 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                         uint32_t pk[16];
 #pragma unroll
                         for (int e = 0; e < 32; e += 2) {
-                            const float p0 = ex2(fmaf(__uint_as_float(v[cch & 1][e]), c2, -m));
-                            const float p1 = ex2(fmaf(__uint_as_float(v[cch & 1][e + 1]), c2, -m));
-                            ls[0] += p0;
-                            ls[1] += p1;
-                            pk[e >> 1] = pack_bf16(p0, p1);
+                            const float2 x = __ffma2_rn(make_float2(__uint_as_float(v[cch & 1][e]), __uint_as_float(v[cch & 1][e + 1])), c2v, nm);
+                            const float2 pr = make_float2(ex2(x.x), ex2(x.y));
+                            ls = __fadd2_rn(ls, pr);
+                            pk[e >> 1] = pack_bf16(pr.x, pr.y);
                         }
                         // chunk cch of P (16 packed columns) lands on S columns that have been read already
                         tmem_st16(s_addr + 16 * cch, pk);
                     }
-                    lsum = ls[0] + ls[1];
+                    lsum = ls.x + ls.y;
                     SA_PROF_ADD(22 + r, t_p2);
                 } else {
                     // pass 1: row maximum of the valid columns
