@@ -779,10 +779,13 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     const int wq = row >> 5;
                     constexpr bool two_q = TWOQ;                         // DW = 16: two queries per warp
                     const int part_row = two_q ? (wq * 2 + (lane >> 4)) : wq;
-                    float* dq_part = scr_a;                              // [4 or 8 partial rows][HD]
+                    float* dq_part = scr_a;                              // [4 partial rows][HD] when a query spans several warps
+                    const int ppq = two_q ? 1 : (DW >> 5);               // partial rows (warps) per query
+                    __nv_bfloat16* dq_out = dq == nullptr ? nullptr : dq + ri.b * p.dq.b + (long)i0 * p.dq.n + ri.h * p.dq.h;
                     const int slot = row_valid ? kb % max(ring_rows, 1) : 0;
                     // Rows that are not valid (delta >= w2, K2 row before the buffer, query past the end) have
                     // P = dS = 0, hence exact zeros in U and G: they need no masking in the sums below.
+                    SA_PROF_ADD(28 + grp, t_epi);
 #pragma unroll 1
                     for (int ph = 0; ph < 4; ++ph) {
                         const int c = (wq + ph) & 3;
@@ -810,7 +813,13 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             }
                             if constexpr (!two_q) {
                                 const float tot = warp_transpose_reduce<CW>(v, lane) * mult;
-                                if (lane < CW) dq_part[part_row * HD + c * CW + lane] = tot;
+                                if (lane < CW) {
+                                    if (ppq == 1) {      // the warp holds the whole query: its dQ columns are final
+                                        if (i0 + wq < p.N) dq_out[(long)wq * p.dq.n + c * CW + lane] = __float2bfloat16_rn(tot);
+                                    } else {
+                                        dq_part[part_row * HD + c * CW + lane] = tot;
+                                    }
+                                }
                             } else {
 #pragma unroll
                                 for (int hb = 0; hb < CW / 16; ++hb) {
@@ -818,7 +827,8 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 #pragma unroll
                                     for (int e = 0; e < 16; ++e) vv[e] = v[16 * hb + e];
                                     const float tot = half_warp_transpose_reduce16(vv, lane) * mult;
-                                    dq_part[part_row * HD + c * CW + 16 * hb + (lane & 15)] = tot;
+                                    if (i0 + part_row < p.N)
+                                        dq_out[(long)part_row * p.dq.n + c * CW + 16 * hb + (lane & 15)] = __float2bfloat16_rn(tot);
                                 }
                             }
                         }
@@ -846,9 +856,9 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         named_barrier_sync(1 + grp, 128);
                         SA_PROF_ADD(53 + 4 * grp, t_p3);
                     }
-                    if (grp == 0 && dq != nullptr) {
-                        // partial rows per query: DW / 32 warps, or one half warp; thread t finishes column t
-                        const int ppq = two_q ? 1 : (DW >> 5);
+                    SA_PROF_T0(t_dqf);
+                    if (grp == 0 && dq != nullptr && ppq > 1) {
+                        // a query spans DW / 32 warps: thread t finishes column t
                         if (row < HD) {
                             for (int q2 = 0; q2 < qpt; ++q2) {
                                 float a = 0.f;
@@ -859,6 +869,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         }
                         named_barrier_sync(1 + grp, 128);
                     }
+                    SA_PROF_ADD(24 + grp, t_dqf);
                 } else {
                 // ---- general path (several queries per warp, or no room for the ring): stage the scaled
                 // rows in shared memory and sum them per output row
@@ -929,22 +940,29 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     named_barrier_sync(1 + grp, 128);
                 }
                 }
+                SA_PROF_T0(t_flush);
                 if (need_kv2 && ring_rows > 0) {
                     // rows no later query of the run reaches are final: move them to the workspace, clear the slots
                     const bool last_unit = i0 + qpt >= ri.i_run1;
                     const int f_hi = last_unit ? kb_max + 1 : max(0, i0 + qpt + p.halo2 - (p.w2 - 1));
-                    for (int kbf = flush_lo; kbf < f_hi; ++kbf) {
+                    // each warp moves whole rows, a lane four consecutive columns of them
+                    for (int kbf = flush_lo + (row >> 5); kbf < f_hi; kbf += 4) {
                         const int slot = kbf % ring_rows;
                         float* dst = (kbf >= own0) ? ws_full + (bh * p.N + (kbf - p.halo2)) * HD
                                                    : ws_head + ((bh * P.num_runs + ri.run) * (p.w2 - 1) + (kbf - (own0 - (p.w2 - 1)))) * HD;
-                        for (int d = row; d < HD; d += 128) {
-                            float* src = ring + ring_index<HD>(slot, d);
-                            dst[d] = *src * mult;          // the ring holds unscaled sums
-                            *src = 0.f;
+                        float* src = ring + ring_index<HD>(slot, 0);
+                        for (int d = lane * 4; d < HD; d += 128) {
+                            // the ring holds unscaled sums
+                            *(float4*)(dst + d) = make_float4(src[d] * mult, src[d + 1] * mult, src[d + 2] * mult, src[d + 3] * mult);
+                            src[d] = 0.f;
+                            src[d + 1] = 0.f;
+                            src[d + 2] = 0.f;
+                            src[d + 3] = 0.f;
                         }
                     }
                     flush_lo = max(flush_lo, f_hi);
                 }
+                SA_PROF_ADD(26 + grp, t_flush);
                 SA_PROF_ADD(44 + grp, t_epi);
                 tc_fence_before();
                 mbar_arrive(B.acc_free);
