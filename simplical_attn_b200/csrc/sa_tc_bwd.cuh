@@ -31,6 +31,8 @@
 // tiles, four tiles ahead of their use), warp 8: MMA issuer, warp 9: TMA issuer.
 #pragma once
 
+#include <type_traits>
+
 #include "sa_ptx.cuh"
 
 namespace sa {
@@ -328,27 +330,35 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 SA_PROF_T0(t_csm);
                 if (P.dw_log2 >= 4) {
                     // 16 columns (virtual rows) at a time, each chunk within one query; the next chunk's
-                    // tensor-memory loads are in flight while the current one is processed
-                    uint32_t s[2][16], dp[2][16];
-                    tmem_ld16(tm_s + lane_addr + 64 * grp, s[0]);
-                    tmem_ld16(tm_dp + lane_addr + 64 * grp, dp[0]);
+                    // tensor-memory loads are in flight while the current one is processed.  A step whose
+                    // columns all lie inside the window of every row of the warp needs no masks.
+                    const int i_first = (int)((rho0 + 64 * grp) >> P.dw_log2), i_last = (int)((rho0 + 64 * grp + 63) >> P.dw_log2);
+                    const bool step_full = __all_sync(0xffffffffu, jb <= i_first + p.halo1 && jb >= i_last + p.halo1 - p.w1 + 1);
+                    auto run_step = [&](auto masked_tag) {
+                        constexpr bool MASKED = decltype(masked_tag)::value;
+                        uint32_t s[2][16], dp[2][16];
+                        tmem_ld16(tm_s + lane_addr + 64 * grp, s[0]);
+                        tmem_ld16(tm_dp + lane_addr + 64 * grp, dp[0]);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const int c0 = 64 * grp + 16 * k;
-                        tmem_wait_ld();
-                        if (k + 1 < 4) {
-                            tmem_ld16(tm_s + lane_addr + c0 + 16, s[(k + 1) & 1]);
-                            tmem_ld16(tm_dp + lane_addr + c0 + 16, dp[(k + 1) & 1]);
+                        for (int k = 0; k < 4; ++k) {
+                            const int c0 = 64 * grp + 16 * k;
+                            tmem_wait_ld();
+                            if (k + 1 < 4) {
+                                tmem_ld16(tm_s + lane_addr + c0 + 16, s[(k + 1) & 1]);
+                                tmem_ld16(tm_dp + lane_addr + c0 + 16, dp[(k + 1) & 1]);
+                            }
+                            const int i = (int)((rho0 + c0) >> P.dw_log2);
+                            const bool valid = !MASKED || ((jb <= i + p.halo1) && (jb >= i + p.halo1 - p.w1 + 1));
+                            uint32_t pp[8], ds[8];
+                            softmax_bwd_chunk<MASKED, 16>(s[k & 1], dp[k & 1], 0, valid ? 0 : 1, valid ? 15 : 0, c2, m_lse[i - iq0],
+                                                          m_delta[i - iq0], pp, ds);
+                            // packed P^T / dS^T of columns [64g + 16k, +16) go to tensor-memory columns 64g + 8k ...
+                            tmem_st8(tm_s + lane_addr + 64 * grp + 8 * k, pp);
+                            tmem_st8(tm_dp + lane_addr + 64 * grp + 8 * k, ds);
                         }
-                        const int i = (int)((rho0 + c0) >> P.dw_log2);
-                        const bool valid = (jb <= i + p.halo1) && (jb >= i + p.halo1 - p.w1 + 1);
-                        uint32_t pp[8], ds[8];
-                        softmax_bwd_chunk<true, 16>(s[k & 1], dp[k & 1], 0, valid ? 0 : 1, valid ? 15 : 0, c2, m_lse[i - iq0],
-                                                    m_delta[i - iq0], pp, ds);
-                        // packed P^T / dS^T of columns [64g + 16k, +16) go to tensor-memory columns 64g + 8k ...
-                        tmem_st8(tm_s + lane_addr + 64 * grp + 8 * k, pp);
-                        tmem_st8(tm_dp + lane_addr + 64 * grp + 8 * k, ds);
-                    }
+                    };
+                    if (step_full) run_step(std::false_type{});
+                    else run_step(std::true_type{});
                 } else {
 #pragma unroll 1
                     for (int cc = 0; cc < 64; cc += 16) {
