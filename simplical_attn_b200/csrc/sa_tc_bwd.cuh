@@ -308,7 +308,8 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 
     if (warp < 8) {
         // ---------------------------------------------------------------- softmax groups + epilogue
-        reg_alloc<104>();      // 2 x 104 + 2 x 96 (producers) + 80 = 5 x 96: an increase beyond the block's own pool would never return
+        // Register pool of the block: 640 x 96 = 2 x 96 (softmax groups, unchanged) + 2 x 112 (producers) + 64
+        // (MMA / TMA group): an increase beyond the block's own pool would never return.
         const int grp = warp >> 2;
         const int row = tid & 127;                       // tensor-memory lane = K1/V1 row of the block's tile
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
@@ -428,6 +429,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         }
     } else if (warp < 16) {
         // ---------------------------------------------------------------- producers: group 0 forms A, group 1 forms C
+        reg_alloc<112>();
         const int grp = (warp - 8) >> 2;
         const int row = tid & 127;
         uint32_t g_base = 0;
@@ -449,6 +451,16 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const int64_t ys = grp == 0 ? p.k2.n : p.v2.n;
                 const float bias = BIAS ? (grp == 0 ? p.k2_bias : p.v2_bias) : 0.f;
                 const int iq0 = (int)(rho0 >> P.dw_log2);
+                // LSE2 and Delta of the tile's queries: loaded before the tile is formed so that the
+                // latency of these few loads is not added behind it
+                const int nq = max(1, kColTileRows >> P.dw_log2);
+                const bool has_meta = grp == 0 && row < nq;
+                float meta_lse = INFINITY, meta_delta = 0.f;
+                if (has_meta && iq0 + row < p.N) {
+                    const long li = ((long)ci.b * p.H + h) * p.N + iq0 + row;
+                    meta_lse = P.lse2[li];
+                    meta_delta = P.delta[li];
+                }
                 switch (P.dw_log2) {     // whole queries per tile: share the K2 / V2 rows between them
                     case 4: form_product_tile_shared<HD, 4, BIAS>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
                     case 5: form_product_tile_shared<HD, 5, BIAS>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
@@ -457,16 +469,10 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         form_product_tile<HD, kColTileRows, 128, BIAS>(tile, L::kSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2, xb, xs,
                                                                  yb, ys, bias);
                 }
-                if (grp == 0) {
-                    // LSE2 and Delta of the tile's queries
-                    const int nq = max(1, kColTileRows >> P.dw_log2);
-                    if (row < nq) {
-                        const int i = iq0 + row;
-                        float* m_lse = (float*)(smem + L::kMeta) + stage * 256;
-                        const long li = ((long)ci.b * p.H + h) * p.N + min(i, p.N - 1);
-                        m_lse[row] = (i < p.N) ? P.lse2[li] : INFINITY;
-                        m_lse[128 + row] = (i < p.N) ? P.delta[li] : 0.f;
-                    }
+                if (has_meta) {
+                    float* m_lse = (float*)(smem + L::kMeta) + stage * 256;
+                    m_lse[row] = meta_lse;
+                    m_lse[128 + row] = meta_delta;
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(&st_full[stage]);
@@ -477,7 +483,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         }
     } else if (warp == 16) {
         // ---------------------------------------------------------------- MMA issuer
-        reg_dealloc<80>();
+        reg_dealloc<64>();
         {
             const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
             uint32_t g_base = 0, n_items = 0;
@@ -535,7 +541,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         __syncwarp();
     } else if (warp == 17) {
         // ---------------------------------------------------------------- TMA: the block's K1 / V1 rows
-        reg_dealloc<80>();
+        reg_dealloc<64>();
         if (lane == 0) {
             prefetch_tensormap(&map_k1);
             prefetch_tensormap(&map_v1);
@@ -555,7 +561,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         }
         __syncwarp();
     } else {
-        reg_dealloc<80>();
+        reg_dealloc<64>();
     }
     tc_fence_before();
     __syncthreads();
