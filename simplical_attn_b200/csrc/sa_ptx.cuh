@@ -440,19 +440,27 @@ __device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab
     SA_PROF_ADD(60, t_ld);
     SA_PROF_T0(t_st);
 #endif
+    // Row r = q2 * DW + delta of the tile, delta = DW - 1 + q2 - w, w = pr + k * RPP.  DW and RPP are
+    // multiples of 8, so the swizzle term (r & 7) = (q2 + 7 - pr) & 7 does not depend on the pass:
+    // one base address per query, the passes are constant offsets from it.
+    static_assert(RPP % 8 == 0 && DW % 8 == 0, "the 128-byte swizzle phase must not depend on the pass");
+    const int lim = w2 < DW ? w2 : DW;
+    uint8_t* const base = tile + (c >> 3) * slab_bytes + 128 * (DW - 1 - pr);
 #pragma unroll
-    for (int k = 0; k < PASSES; ++k) {
-        const int w = pr + k * RPP;
-        const int kb = kb_first + w;
+    for (int q2 = 0; q2 < NQ; ++q2) {
+        uint8_t* const bq = base + 128 * (DW + 1) * q2 + ((((c & 7) ^ ((q2 + 7 - pr) & 7))) << 4);
+        const bool q_ok = i0 + q2 < n_q;
 #pragma unroll
-        for (int q2 = 0; q2 < NQ; ++q2) {
-            const int dlt = DW - 1 + q2 - w;
-            if (dlt < 0 || dlt >= DW) continue;
-            const int r = q2 * DW + dlt;
+        for (int k = 0; k < PASSES; ++k) {
+            const int dlt = DW - 1 + q2 - pr - k * RPP;
+            if ((unsigned)dlt >= (unsigned)DW) continue;          // this window row does not meet query q2
+            // x and y chunks of rows outside the tensors were loaded as zeros: without a bias their
+            // product is already the zero the tile needs there
+            bool ok = dlt < lim;
+            if (BIAS) ok = ok && q_ok && (kb_first + pr + k * RPP >= 0);
             uint4 out = make_uint4(0, 0, 0, 0);
-            if (i0 + q2 < n_q && dlt < w2 && kb >= 0)
-                out = BIAS ? mul_chunk(xa[q2], ya[k], bias) : mul_chunk_nobias(xa[q2], ya[k]);
-            *(uint4*)(tile + (c >> 3) * slab_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = out;
+            if (ok) out = BIAS ? mul_chunk(xa[q2], ya[k], bias) : mul_chunk_nobias(xa[q2], ya[k]);
+            *(uint4*)(bq - 128 * RPP * k) = out;
         }
     }
 #ifdef SA_PROFILE
