@@ -638,12 +638,12 @@ __device__ __forceinline__ void load_bf16_cw(const __nv_bfloat16* row, int col, 
 }
 
 
-// Index into a ring of fp32 rows [slot][HD + 1]: the odd row pitch puts the same column of 32
-// consecutive rows into 32 different banks, and a column offset known at compile time stays an
-// immediate in the address.
+// Index into a ring of fp32 rows [slot][HD + 2]: with this row pitch the same column pair of 32
+// consecutive rows falls into different banks for 8-byte accesses, a column offset known at compile
+// time stays an immediate in the address, and rows stay 8-byte aligned.
 template <int HD>
 __device__ __forceinline__ int ring_index(int slot, int col) {
-    return slot * (HD + 1) + col;
+    return slot * (HD + 2) + col;
 }
 
 template <int HD, int NS, bool TWOQ, bool BIAS>
@@ -710,8 +710,8 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         float* scr_b = scr_a + 128 * CW;
         // fp32 accumulators of the dK2 (group 0) / dV2 (group 1) rows currently within reach of the
         // block's queries, one slot per row modulo ring_rows; ring_rows == 0: not enough shared memory
-        float* ring = (float*)(smem + L::kRing) + grp * ring_rows * (HD + 1);
-        for (int x = row; x < ring_rows * (HD + 1); x += 128) ring[x] = 0.f;
+        float* ring = (float*)(smem + L::kRing) + grp * ring_rows * (HD + 2);
+        for (int x = row; x < ring_rows * (HD + 2); x += 128) ring[x] = 0.f;
         named_barrier_sync(1 + grp, 128);
         int flush_lo = 0;
         uint32_t n_mine = 0, n_units = 0;
@@ -817,8 +817,10 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             if constexpr (!BIAS) {
 #pragma unroll
                                 for (int e = 0; e < CW; e += 2) {
-                                    v[e] = __uint_as_float(g[e]) * bf16_lo(xw[e >> 1]);
-                                    v[e + 1] = __uint_as_float(g[e + 1]) * bf16_hi(xw[e >> 1]);
+                                    const float2 t = __fmul2_rn(make_float2(__uint_as_float(g[e]), __uint_as_float(g[e + 1])),
+                                                                make_float2(bf16_lo(xw[e >> 1]), bf16_hi(xw[e >> 1])));
+                                    v[e] = t.x;
+                                    v[e + 1] = t.y;
                                 }
                             } else {
 #pragma unroll
@@ -854,16 +856,16 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         // a warp, lanes (q, delta) and (q+1, delta+1) own the same K2 row: the halves take turns.
                         for (int turn = 0; turn < (two_q ? 2 : 1); ++turn) {
                             if (need_kv2 && row_valid && (!two_q || (lane >> 4) == turn)) {
-                                float acc_r[CW];
+                                float2* rp = (float2*)(ring + ring_index<HD>(slot, c * CW));
+                                float2 acc_r[CW / 2];
 #pragma unroll
-                                for (int e = 0; e < CW; ++e) acc_r[e] = ring[ring_index<HD>(slot, c * CW + e)];
+                                for (int e = 0; e < CW / 2; ++e) acc_r[e] = rp[e];
 #pragma unroll
-                                for (int e = 0; e < CW; e += 2) {
-                                    acc_r[e] = fmaf(__uint_as_float(g[e]), bf16_lo(yw[e >> 1]), acc_r[e]);
-                                    acc_r[e + 1] = fmaf(__uint_as_float(g[e + 1]), bf16_hi(yw[e >> 1]), acc_r[e + 1]);
-                                }
+                                for (int e = 0; e < CW / 2; ++e)
+                                    acc_r[e] = __ffma2_rn(make_float2(__uint_as_float(g[2 * e]), __uint_as_float(g[2 * e + 1])),
+                                                          make_float2(bf16_lo(yw[e]), bf16_hi(yw[e])), acc_r[e]);
 #pragma unroll
-                                for (int e = 0; e < CW; ++e) ring[ring_index<HD>(slot, c * CW + e)] = acc_r[e];
+                                for (int e = 0; e < CW / 2; ++e) rp[e] = acc_r[e];
                             }
                             if (two_q) __syncwarp();
                         }
@@ -1216,7 +1218,7 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         const int ring_want = (1 << pl.dw_log2) + pl.qpt;
         auto launch_row = [&](auto kern, int k_ring, int k_min, int max_dyn, int hd) -> bool {
             int ring_rows = ring_want;
-            int smem = k_ring + 1024 + 2 * ring_rows * (hd + 1) * 4;
+            int smem = k_ring + 1024 + 2 * ring_rows * (hd + 2) * 4;
             if (!need_kv2 || smem > max_dyn) { ring_rows = 0; smem = k_ring + 1024; }
             if (smem < k_min) smem = k_min;
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn) != cudaSuccess) return false;
@@ -1228,7 +1230,7 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         if (k.D == 128) {
             using L3 = BwdSmem<128, 3>;
             using L2 = BwdSmem<128, 2>;
-            const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 129 * 4 <= L3::kMaxDynamic;
+            const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 130 * 4 <= L3::kMaxDynamic;
             if (pl.dw_log2 == 4)
                 ok = launch_row(has_bias ? bwd_row_kernel<128, 3, true, true> : bwd_row_kernel<128, 3, true, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128);
             else
@@ -1237,7 +1239,7 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         } else {
             using L3 = BwdSmem<64, 3>;
             using L2 = BwdSmem<64, 2>;
-            const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 65 * 4 <= L3::kMaxDynamic;
+            const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 66 * 4 <= L3::kMaxDynamic;
             if (pl.dw_log2 == 4)
                 ok = launch_row(has_bias ? bwd_row_kernel<64, 3, true, true> : bwd_row_kernel<64, 3, true, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64);
             else

@@ -463,8 +463,14 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                     float y[32];
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
-                        y[e] = row_valid ? __uint_as_float(v[e]) * wrow * (bf16_lo(vw[16 * cch + (e >> 1)]) + v2_bias) : 0.f;
-                        y[e + 1] = row_valid ? __uint_as_float(v[e + 1]) * wrow * (bf16_hi(vw[16 * cch + (e >> 1)]) + v2_bias) : 0.f;
+                        // rows that are not valid have T = 0 exactly (their P is 0) and wrow = 0: no select needed
+                        const uint32_t w = vw[16 * cch + (e >> 1)];
+                        float2 x2 = make_float2(bf16_lo(w), bf16_hi(w));
+                        if (BIAS) x2 = __fadd2_rn(x2, make_float2(v2_bias, v2_bias));
+                        const float2 y2 = __fmul2_rn(make_float2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])),
+                                                     __fmul2_rn(x2, make_float2(wrow, wrow)));
+                        y[e] = y2.x;
+                        y[e + 1] = y2.y;
                     }
                     tot[cch] = warp_transpose_reduce<32>(y, lane);
                 }
