@@ -244,7 +244,7 @@ struct ColSmem {
     static constexpr int kStream = 2 * kTile;
     static constexpr int kMeta = kStream + kColStages * 2 * kTile;
     static constexpr int kBars = kMeta + kColStages * 256 * 4;
-    static constexpr int kNumBars = 2 * kColStages + 6;
+    static constexpr int kNumBars = 2 * kColStages + 10;
     static constexpr int kMisc = kBars + kNumBars * 8;
     static constexpr int kTotal = kMisc + 16;
     static constexpr int kAlloc = (kTotal + 1024 > 120 * 1024) ? kTotal + 1024 : 120 * 1024;
@@ -271,7 +271,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     uint64_t* st_full = bars;                         // [kColStages] A and C of a tile formed (256 arrivals)
     uint64_t* st_empty = bars + kColStages;           // [kColStages] tile consumed (commit)
     uint64_t* sdp_ready = bars + 2 * kColStages;      // S^T, dP^T computed (commit)
-    uint64_t* pds_ready = sdp_ready + 1;              // P^T, dS^T stored (256 arrivals)
+    uint64_t* pds_ready = sdp_ready + 6;              // [4] P^T, dS^T of the k-th 16-column chunk of both groups stored (256 arrivals)
     uint64_t* stat_full = sdp_ready + 2;              // K1, V1 landed (TMA)
     uint64_t* stat_empty = sdp_ready + 3;             // K1, V1 no longer read (commit)
     uint64_t* acc_ready = sdp_ready + 4;              // dV1, dK1 final (commit)
@@ -288,7 +288,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
             mbar_init(&st_empty[s], 1);
         }
         mbar_init(sdp_ready, 1);
-        mbar_init(pds_ready, 256);
+        for (int k = 0; k < 4; ++k) mbar_init(&pds_ready[k], 256);
         mbar_init(stat_full, 1);
         mbar_init(stat_empty, 1);
         mbar_init(acc_ready, 1);
@@ -356,6 +356,10 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             // packed P^T / dS^T of columns [64g + 16k, +16) go to tensor-memory columns 64g + 8k ...
                             tmem_st8(tm_s + lane_addr + 64 * grp + 8 * k, pp);
                             tmem_st8(tm_dp + lane_addr + 64 * grp + 8 * k, ds);
+                            // the accumulating MMAs of this chunk start while the next one is processed
+                            tmem_wait_st();
+                            tc_fence_before();
+                            mbar_arrive(&pds_ready[k]);
                         }
                     };
                     if (step_full) run_step(std::false_type{});
@@ -384,11 +388,11 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         }
                         tmem_st8(tm_s + lane_addr + 64 * grp + (cc >> 1), pp);
                         tmem_st8(tm_dp + lane_addr + 64 * grp + (cc >> 1), ds);
+                        tmem_wait_st();
+                        tc_fence_before();
+                        mbar_arrive(&pds_ready[cc >> 4]);
                     }
                 }
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(pds_ready);
                 SA_PROF_ADD(28, t_csm);
             }
             g_base += nt;
@@ -519,16 +523,24 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     }
                     tc_commit(leader, sdp_ready);
                     SA_PROF_ADD(29, t_ci1);
-                    mbar_wait(pds_ready, g & 1, wctx, 26);
-                    tc_fence_after();
                     SA_PROF_T0(t_ci2);
-                    // dV1 += P^T-tile C-tile,  dK1 += dS^T-tile A-tile   (K = 128 virtual rows: 8 steps of 16)
+                    // dV1 += P^T-tile C-tile,  dK1 += dS^T-tile A-tile   (K = 128 virtual rows: 8 steps of 16).
+                    // Chunk k of both softmax groups (k-steps k and 4 + k) is issued as soon as it is stored.
 #pragma unroll
-                    for (int kk = 0; kk < kColTileRows / 16; ++kk)
-                        mma_ts(leader, tm_dv1, tm_s + (kk >> 2) * 64 + (kk & 3) * 8, d_cm + kk * (2048 >> 4), idesc_acc, t > 0 || kk > 0);
+                    for (int k = 0; k < 4; ++k) {
+                        mbar_wait(&pds_ready[k], g & 1, wctx, 26);
+                        tc_fence_after();
 #pragma unroll
-                    for (int kk = 0; kk < kColTileRows / 16; ++kk)
-                        mma_ts(leader, tm_dk1, tm_dp + (kk >> 2) * 64 + (kk & 3) * 8, d_am + kk * (2048 >> 4), idesc_acc, t > 0 || kk > 0);
+                        for (int gq = 0; gq < 2; ++gq) {
+                            const int kk = 4 * gq + k;
+                            mma_ts(leader, tm_dv1, tm_s + gq * 64 + k * 8, d_cm + kk * (2048 >> 4), idesc_acc, t > 0 || k > 0 || gq > 0);
+                        }
+#pragma unroll
+                        for (int gq = 0; gq < 2; ++gq) {
+                            const int kk = 4 * gq + k;
+                            mma_ts(leader, tm_dk1, tm_dp + gq * 64 + k * 8, d_am + kk * (2048 >> 4), idesc_acc, t > 0 || k > 0 || gq > 0);
+                        }
+                    }
                     tc_commit(leader, &st_empty[stage]);
                     SA_PROF_ADD(36, t_ci2);
                 }

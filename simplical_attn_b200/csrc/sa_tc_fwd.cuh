@@ -344,9 +344,10 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                         tmem_wait_ld();
                         if (cch + 1 < 4) tmem_ld32(s_addr + 32 * (cch + 1), v[(cch + 1) & 1]);
 #pragma unroll
-                        for (int e = 0; e < 32; e += 4) {
+                        for (int e = 0; e < 32; e += 8) {
 #pragma unroll
-                            for (int x = 0; x < 4; ++x) mx[x] = fmaxf(mx[x], __uint_as_float(v[cch & 1][e + x]));
+                            for (int x = 0; x < 4; ++x)
+                                mx[x] = max3(mx[x], __uint_as_float(v[cch & 1][e + x]), __uint_as_float(v[cch & 1][e + 4 + x]));
                         }
                     }
                     SA_PROF_ADD(20 + r, t_sm);
