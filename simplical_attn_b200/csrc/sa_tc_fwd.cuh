@@ -51,7 +51,7 @@ struct FwdSmem {
     static constexpr int kV1 = kK1 + kStages * kTileBytes;       // kStages tiles
     static constexpr int kStats = kV1 + kStages * kTileBytes;    // m, l: 2 groups x 128 x 2 floats
     static constexpr int kBars = kStats + kNumRowTiles * kRowTile * 2 * 4;
-    static constexpr int kNumBars = 4 * kStages + 4 * kNumRowTiles;
+    static constexpr int kNumBars = 4 * kStages + 7 * kNumRowTiles;
     static constexpr int kMisc = kBars + kNumBars * 8;           // tmem base, abort flag
     static constexpr int kScratch = kMisc + 16;                  // only used when HD == 64
     static constexpr int kScratchBytes = (HD == 64) ? kNumRowTiles * kRowTile * 32 * 4 : 0;
@@ -107,8 +107,8 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
     uint64_t* v1_empty = bars + 3 * kStages;
     uint64_t* a_ready = bars + 4 * kStages;         // [kNumRowTiles]
     uint64_t* s_ready = a_ready + kNumRowTiles;
-    uint64_t* p_ready = s_ready + kNumRowTiles;
-    uint64_t* o_ready = p_ready + kNumRowTiles;
+    uint64_t* o_ready = s_ready + kNumRowTiles;
+    uint64_t* p_ready = o_ready + kNumRowTiles;     // [kNumRowTiles][4]: P of one 32-column chunk stored
     uint32_t* tmem_base_slot = (uint32_t*)(smem + L::kMisc);
     volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
     const WaitCtx wctx{abort_flag, P.status};
@@ -128,7 +128,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
         for (int r = 0; r < kNumRowTiles; ++r) {
             mbar_init(&a_ready[r], kRowTile);
             mbar_init(&s_ready[r], 1);
-            mbar_init(&p_ready[r], kRowTile);
+            for (int c = 0; c < 4; ++c) mbar_init(&p_ready[4 * r + c], kRowTile);
             mbar_init(&o_ready[r], 1);
         }
         *abort_flag = 0;
@@ -202,17 +202,20 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                     }
                     tc_commit(leader, &s_ready[r]);
                 };
-                auto issue_pv = [&](int r, int t) {
+                // P arrives in two halves of 64 columns (four k-steps each): the MMAs of a chunk are issued as
+                // soon as it is stored, while the softmax group works on the next one.
+                auto issue_pv = [&](int r, int t, uint32_t parity, uint32_t gt) {
                     const int s = (g + t) % kStages;
                     const uint64_t db = desc_mnmajor(smem_base + L::kV1 + s * L::kTileBytes, L::kSlabBytes);
-                    if (t != ug.ntiles - 1) {
+                    const int ksteps = (t != ug.ntiles - 1) ? kColTile / 16 : ug.last_width / 16;
 #pragma unroll
-                        for (int kk = 0; kk < kColTile / 16; ++kk)
-                            mma_ts(leader, tmem_t[r], tmem_s[r] + kk * 8, db + kk * (2048 >> 4), idesc_pv, t > 0 || kk > 0);
-                    } else {
-                        const int ksteps = ug.last_width / 16;
-                        for (int kk = 0; kk < ksteps; ++kk)
-                            mma_ts(leader, tmem_t[r], tmem_s[r] + kk * 8, db + kk * (2048 >> 4), idesc_pv, t > 0 || kk > 0);
+                    for (int c = 0; c < 2; ++c) {
+                        mbar_wait(&p_ready[4 * r + c], parity, wctx, 5);
+                        if (c == 0 && r == 0) mbar_wait(&v1_full[gt % kStages], (gt / kStages) & 1, wctx, 6);
+                        tc_fence_after();
+#pragma unroll
+                        for (int kk = 4 * c; kk < 4 * c + 4; ++kk)
+                            if (kk < ksteps) mma_ts(leader, tmem_t[r], tmem_s[r] + kk * 8, db + kk * (2048 >> 4), idesc_pv, t > 0 || kk > 0);
                     }
                 };
                 // prologue: S(0) of both row tiles
@@ -226,12 +229,9 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                 for (int t = 0; t < ug.ntiles; ++t) {
                     const uint32_t gt = g + t;
                     for (int r = 0; r < kNumRowTiles; ++r) {
-                        mbar_wait(&p_ready[r], ns[r] & 1, wctx, 5);
-                        ++ns[r];
-                        if (r == 0) mbar_wait(&v1_full[gt % kStages], (gt / kStages) & 1, wctx, 6);
-                        tc_fence_after();
                         SA_PROF_T0(t_pv);
-                        issue_pv(r, t);
+                        issue_pv(r, t, ns[r] & 1, gt);
+                        ++ns[r];
                         SA_PROF_ADD(30, t_pv);
                         if (r == kNumRowTiles - 1) tc_commit(leader, &v1_empty[gt % kStages]);
                         if (t + 1 < ug.ntiles) {
@@ -371,6 +371,11 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                         }
                         // chunk cch of P (16 packed columns) lands on S columns that have been read already
                         tmem_st16(s_addr + 16 * cch, pk);
+                        if (cch & 1) {       // a half tile of P is complete
+                            tmem_wait_st();
+                            tc_fence_before();
+                            mbar_arrive(&p_ready[4 * r + (cch >> 1)]);
+                        }
                     }
                     lsum = ls.x + ls.y;
                     SA_PROF_ADD(22 + r, t_p2);
@@ -407,14 +412,13 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                         }
                         tmem_st16(s_addr + (c0 >> 1), pk);
                     }
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(&p_ready[4 * r]);
+                    mbar_arrive(&p_ready[4 * r + 1]);
                     SA_PROF_ADD((t == 0 ? 24 : 26) + r, t_sm);
                 }
                 l += lsum;
-                SA_PROF_T0(t_st);
-                tmem_wait_st();
-                tc_fence_before();
-                mbar_arrive(&p_ready[r]);
-                SA_PROF_ADD(28 + r, t_st);
                 SA_PROF_ADD(16 + r, t_sm);
             }
             // ---- epilogue: merge the delta rows of each query
