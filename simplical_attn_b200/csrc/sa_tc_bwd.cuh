@@ -1097,37 +1097,47 @@ __global__ void __launch_bounds__(256)
 kv2_reduce_kernel(BwdTcParams P, __nv_bfloat16* __restrict__ dk2, __nv_bfloat16* __restrict__ dv2) {
     const KParams& p = P.k;
     const int HD = p.D;
-    const long total = (long)p.B * p.n2 * p.Hkv * (HD / 2);
+    const int cpr = HD / 4;                               // threads per row: four columns (16 bytes of fp32) each
+    const long total = (long)p.B * p.n2 * p.Hkv * cpr;
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
-    const int d = (int)(idx % (HD / 2)) * 2;
-    const int hk = (int)((idx / (HD / 2)) % p.Hkv);
-    const int kb = (int)((idx / (HD / 2) / p.Hkv) % p.n2);
-    const int b = (int)(idx / (HD / 2) / p.Hkv / p.n2);
+    const int d = (int)(idx % cpr) * 4;
+    const int hk = (int)((idx / cpr) % p.Hkv);
+    const int kb = (int)((idx / cpr / p.Hkv) % p.n2);
+    const int b = (int)(idx / cpr / p.Hkv / p.n2);
     const int runq = P.units_per_run * (128 >> P.dw_log2);
     const int ip = kb - p.halo2;                          // the query aligned with this row (may be negative)
     // runs r with  r*runq in [ip + 1, ip + w2 - 1]
     int r_lo = (ip + 1 <= 0) ? 0 : (ip + 1 + runq - 1) / runq;
     int r_hi = (ip + p.w2 - 1 < 0) ? -1 : (ip + p.w2 - 1) / runq;
     if (r_hi > P.num_runs - 1) r_hi = P.num_runs - 1;
-    float2 ak = make_float2(0.f, 0.f), av = make_float2(0.f, 0.f);
+    float4 ak = make_float4(0.f, 0.f, 0.f, 0.f), av = make_float4(0.f, 0.f, 0.f, 0.f);
+    auto add4 = [](float4& a, const float4 t) { a.x += t.x; a.y += t.y; a.z += t.z; a.w += t.w; };
     for (int hq = 0; hq < p.G; ++hq) {
         const int h = hk * p.G + hq;
         const long bh = (long)b * p.H + h;
         if (ip >= 0 && ip < p.N) {
             const long o = (bh * p.N + ip) * HD + d;
-            if (dk2) { const float2 t = *(const float2*)(P.ws_full_k2 + o); ak.x += t.x; ak.y += t.y; }
-            if (dv2) { const float2 t = *(const float2*)(P.ws_full_v2 + o); av.x += t.x; av.y += t.y; }
+            if (dk2) add4(ak, __ldcs((const float4*)(P.ws_full_k2 + o)));     // read once: streaming loads
+            if (dv2) add4(av, __ldcs((const float4*)(P.ws_full_v2 + o)));
         }
         for (int r = r_lo; r <= r_hi; ++r) {
             const int slot = kb - (r * runq + p.halo2 - (p.w2 - 1));
             const long o = ((bh * P.num_runs + r) * (p.w2 - 1) + slot) * HD + d;
-            if (dk2) { const float2 t = *(const float2*)(P.ws_head_k2 + o); ak.x += t.x; ak.y += t.y; }
-            if (dv2) { const float2 t = *(const float2*)(P.ws_head_v2 + o); av.x += t.x; av.y += t.y; }
+            if (dk2) add4(ak, *(const float4*)(P.ws_head_k2 + o));
+            if (dv2) add4(av, *(const float4*)(P.ws_head_v2 + o));
         }
     }
-    if (dk2) *(__nv_bfloat162*)(dk2 + b * p.dk2.b + (long)kb * p.dk2.n + hk * p.dk2.h + d) = __floats2bfloat162_rn(ak.x, ak.y);
-    if (dv2) *(__nv_bfloat162*)(dv2 + b * p.dv2.b + (long)kb * p.dv2.n + hk * p.dv2.h + d) = __floats2bfloat162_rn(av.x, av.y);
+    if (dk2) {
+        __nv_bfloat162* dst = (__nv_bfloat162*)(dk2 + b * p.dk2.b + (long)kb * p.dk2.n + hk * p.dk2.h + d);
+        dst[0] = __floats2bfloat162_rn(ak.x, ak.y);
+        dst[1] = __floats2bfloat162_rn(ak.z, ak.w);
+    }
+    if (dv2) {
+        __nv_bfloat162* dst = (__nv_bfloat162*)(dv2 + b * p.dv2.b + (long)kb * p.dv2.n + hk * p.dv2.h + d);
+        dst[0] = __floats2bfloat162_rn(av.x, av.y);
+        dst[1] = __floats2bfloat162_rn(av.z, av.w);
+    }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1261,7 +1271,7 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         if (!ok) return SA_ERR_LAUNCH;
         ++*nlaunch;
         if (need_kv2) {
-            const long total = (long)k.B * k.n2 * k.Hkv * (k.D / 2);
+            const long total = (long)k.B * k.n2 * k.Hkv * (k.D / 4);
             kv2_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(P, (__nv_bfloat16*)dk2, (__nv_bfloat16*)dv2);
             ++*nlaunch;
         }
