@@ -1090,6 +1090,341 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 }
 
 // ------------------------------------------------------------------------------------------------
+// 3b. Row kernel with separate epilogue warpgroups, for 32 delta slots per query (w2 in 17..32) when
+//     the dK2/dV2 ring fits: warps 0-7 form the operands and run the softmax, warps 8-15 read U and G
+//     out of tensor memory (dQ, dK2 ring, dV2 ring) while warps 0-7 already work on the next unit, so
+//     the epilogue of a unit overlaps the main loop of the next one.  Same math, same order of
+//     additions, same workspace contents as bwd_row_kernel.
+// ------------------------------------------------------------------------------------------------
+constexpr int kRow2Threads = 640;     // softmax groups (0-7), epilogue groups (8-15), MMA (16), TMA (17), 2 idle
+
+template <int HD, bool BIAS>
+__global__ void __launch_bounds__(kRow2Threads, 1)
+bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
+                const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
+                const __nv_bfloat16* __restrict__ k2, const __nv_bfloat16* __restrict__ v2,
+                const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dq, int need_kv2, int ring_rows) {
+    constexpr int NS = kRowStages;
+    using L = BwdSmem<HD, NS>;
+    using namespace ptx;
+    constexpr int CW = 16;                                // epilogue chunk width
+    constexpr int NPH = HD / CW;                          // epilogue phases
+    constexpr int DWL = 5, DW = 32, QPT = 4;              // delta slots per query, queries per 128-row unit
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t smem_base = smem_u32(smem);
+    const KParams& p = P.k;
+    const BwdBars B = bwd_bars<NS>((uint64_t*)(smem + L::kBars));
+    uint32_t* tmem_slot = (uint32_t*)(smem + L::kMisc);
+    volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
+    const WaitCtx wctx{abort_flag, P.status};
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    SA_PROF_T0(t_life);
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(&B.st_full[s], 1);
+            mbar_init(&B.st_empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&B.sdp_ready[b], 1);
+            mbar_init(&B.pds_ready[b], 128);
+        }
+        mbar_init(B.stat_full, 256);       // A and C formed by the two softmax groups
+        mbar_init(B.stat_empty, 1);        // the unit's last S / dP MMAs have read A and C
+        mbar_init(B.acc_ready, 1);         // U and G final
+        mbar_init(B.acc_free, 256);        // U and G read out by the two epilogue groups
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 16) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tm_s[2] = {tmem_base, tmem_base + 64};
+    const uint32_t tm_dp[2] = {tmem_base + 128, tmem_base + 192};
+    const uint32_t tm_u = tmem_base + 256, tm_g = tmem_base + 384;     // U = P V1, G = dS K1
+
+    // Register pool of the block: 640 x 96 = 2 x 120 (softmax groups) + 2 x 88 (epilogue groups) + 64 (the
+    // rest): an increase beyond the block's own pool would never return.
+    if (warp < 8) {
+        // ---------------------------------------------------------------- operand formation + softmax
+        reg_alloc<120>();
+        const int grp = warp >> 2;
+        const int row = tid & 127;
+        const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
+        const int qq = row >> DWL;
+        const int dlt = row & (DW - 1);
+        const float c2 = p.scale * kLog2e;
+        uint8_t* my_tile = smem + (grp == 0 ? L::kStat0 : L::kStat1);      // group 0 forms A, group 1 forms C
+        uint32_t n_mine = 0, n_units = 0;
+        for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
+            const RowItem ri = row_item(P, it);
+            for (int i0 = ri.i_run0; i0 < ri.i_run1; i0 += QPT, ++n_units) {
+                const RowUnit ru = row_unit(P, i0);
+                const int i = i0 + qq;
+                const int kb = i + p.halo2 - dlt;
+                const bool row_valid = (i < p.N) && (dlt < p.w2) && (kb >= 0);
+                const int ic = min(i, p.N - 1);
+                // ---- stationary operand of this group, once the previous unit's S / dP MMAs have read the old one
+                if (n_units > 0) mbar_wait(B.stat_empty, (n_units - 1) & 1, wctx, 37);
+                SA_PROF_T0(t_form);
+                if (grp == 0)
+                    form_product_tile_shared<HD, DWL, BIAS>(my_tile, L::kBigSlab, row, i0, p.N, p.w2, p.halo2,
+                                                            q + ri.b * p.q.b + ri.h * p.q.h, p.q.n,
+                                                            k2 + ri.b * p.k2.b + ri.hk * p.k2.h, p.k2.n, BIAS ? p.k2_bias : 0.f);
+                else
+                    form_product_tile_shared<HD, DWL, BIAS>(my_tile, L::kBigSlab, row, i0, p.N, p.w2, p.halo2,
+                                                            d_o + ri.b * p.d_o.b + ri.h * p.d_o.h, p.d_o.n,
+                                                            v2 + ri.b * p.v2.b + ri.hk * p.v2.h, p.v2.n, BIAS ? p.v2_bias : 0.f);
+                fence_proxy_async_smem();
+                tc_fence_before();
+                mbar_arrive(B.stat_full);
+                SA_PROF_ADD(40 + grp, t_form);
+                SA_PROF_T0(t_loop);
+                const long li = ((long)ri.b * p.H + ri.h) * p.N + ic;
+                const float lse2 = P.lse2[li], dlt_i = P.delta[li];
+                const int jhi = row_valid ? i + p.halo1 : -1;
+                const int jlo = row_valid ? max(0, i + p.halo1 - p.w1 + 1) : 0;
+                // ---- column tiles of this group
+                for (int t = grp; t < ru.nt; t += 2, ++n_mine) {
+                    const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
+                    const int tile0 = ru.col_start + t * kStreamRows;
+                    const int lo = jlo - tile0, hi = jhi - tile0;
+                    const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= kStreamRows - 1);
+                    mbar_wait(&B.sdp_ready[grp], n_mine & 1, wctx, 30);
+                    tc_fence_after();
+                    SA_PROF_T0(t_rsm);
+#pragma unroll 1
+                    for (int c0 = 0; c0 < width; c0 += 32) {
+                        uint32_t s[32], dp[32], pp[16], ds[16];
+                        tmem_ld32(tm_s[grp] + lane_addr + c0, s);
+                        tmem_ld32(tm_dp[grp] + lane_addr + c0, dp);
+                        tmem_wait_ld();
+                        if (full) softmax_bwd_chunk<false>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
+                        else softmax_bwd_chunk<true>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
+                        tmem_st16(tm_s[grp] + lane_addr + (c0 >> 1), pp);
+                        tmem_st16(tm_dp[grp] + lane_addr + (c0 >> 1), ds);
+                    }
+                    tmem_wait_st();
+                    tc_fence_before();
+                    mbar_arrive(&B.pds_ready[grp]);
+                    SA_PROF_ADD(58 + grp, t_rsm);
+                }
+                SA_PROF_ADD(42 + grp, t_loop);
+            }
+        }
+    } else if (warp < 16) {
+        // ---------------------------------------------------------------- epilogue groups: group g takes columns
+        // [g * HD/2, (g + 1) * HD/2) of all three results (dQ and dK2 from G, dV2 from U), so both groups
+        // carry the same load and no ring column is shared between them
+        reg_dealloc<88>();
+        const int grp = (warp - 8) >> 2;
+        const int row = tid & 127;
+        const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
+        const int qq = row >> DWL;
+        const int dlt = row & (DW - 1);
+        const int wq = row >> 5;                          // warp within the group = query within the unit
+        constexpr int HALF = HD / 2;
+        constexpr int NPHG = HALF / CW;                   // phases per group (4 at HD = 128)
+        static_assert(NPHG == 4, "one column chunk per warp and phase");
+        const int cbase = grp * HALF;
+        // fp32 accumulators of the dK2 / dV2 rows currently within reach of the block's queries, one slot
+        // per row modulo ring_rows
+        float* ring_k = (float*)(smem + L::kRing);
+        float* ring_v = ring_k + ring_rows * (HD + 2);
+        for (int x = row; x < ring_rows * HALF; x += 128) {
+            const int idx = ring_index<HD>(x / HALF, cbase + x % HALF);
+            ring_k[idx] = 0.f;
+            ring_v[idx] = 0.f;
+        }
+        named_barrier_sync(3 + grp, 128);
+        int flush_lo = 0;
+        uint32_t n_units = 0;
+        for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
+            const RowItem ri = row_item(P, it);
+            for (int i0 = ri.i_run0, uidx = 0; i0 < ri.i_run1; i0 += QPT, ++uidx, ++n_units) {
+                const int i = i0 + qq;
+                const int kb = i + p.halo2 - dlt;
+                const bool row_valid = (i < p.N) && (dlt < p.w2) && (kb >= 0);
+                const int ic = min(i, p.N - 1), kc = max(kb, 0);
+                const __nv_bfloat16* q_row = q + ri.b * p.q.b + (long)ic * p.q.n + ri.h * p.q.h + cbase;
+                const __nv_bfloat16* do_row = d_o + ri.b * p.d_o.b + (long)ic * p.d_o.n + ri.h * p.d_o.h + cbase;
+                const __nv_bfloat16* k2_row = k2 + ri.b * p.k2.b + (long)kc * p.k2.n + ri.hk * p.k2.h + cbase;
+                const long bh = (long)ri.b * p.H + ri.h;
+                const int kb_max = min(i0 + QPT, p.N) - 1 + p.halo2;
+                const int own0 = ri.i_run0 + p.halo2;                        // first row owned by this run
+                if (uidx == 0) flush_lo = max(0, own0 - (p.w2 - 1));
+                const int slot = row_valid ? kb % max(ring_rows, 1) : 0;
+                __nv_bfloat16* dq_out = dq == nullptr ? nullptr : dq + ri.b * p.dq.b + (long)i0 * p.dq.n + ri.h * p.dq.h + cbase;
+                mbar_wait(B.acc_ready, n_units & 1, wctx, 31);
+                tc_fence_after();
+                SA_PROF_T0(t_epi);
+                // A warp holds the 32 deltas of one query: within it the lanes own distinct K2 rows.  Warp w works
+                // on column chunk (w + phase) % 4 of the group's half, so no two warps touch the same ring columns
+                // at the same time; the delta sum for dQ is a register exchange inside the warp.  Rows that are
+                // not valid have P = dS = 0, hence exact zeros in U and G: they need no masking in the sums.
+#pragma unroll 1
+                for (int ph = 0; ph < NPHG; ++ph) {
+                    const int c = ((wq + ph) & 3) * CW;
+                    uint32_t qw[CW / 2], ow[CW / 2], xw[CW / 2], g[CW], u[CW];
+                    load_bf16_words<CW>(q_row + c, qw);
+                    load_bf16_words<CW>(do_row + c, ow);
+                    load_bf16_words<CW>(k2_row + c, xw);
+                    tmem_ld16(tm_g + lane_addr + cbase + c, g);
+                    tmem_ld16(tm_u + lane_addr + cbase + c, u);
+                    tmem_wait_ld();
+                    if (dq != nullptr) {
+                        float v[CW];
+#pragma unroll
+                        for (int e = 0; e < CW; e += 2) {
+                            float2 x2 = make_float2(bf16_lo(xw[e >> 1]), bf16_hi(xw[e >> 1]));
+                            if (BIAS) x2 = __fadd2_rn(x2, make_float2(p.k2_bias, p.k2_bias));
+                            const float2 t = __fmul2_rn(make_float2(__uint_as_float(g[e]), __uint_as_float(g[e + 1])), x2);
+                            v[e] = t.x;
+                            v[e + 1] = t.y;
+                        }
+                        const float tot = warp_transpose_reduce<CW>(v, lane) * p.scale;
+                        if (lane < CW && i0 + wq < p.N) dq_out[(long)wq * p.dq.n + c + lane] = __float2bfloat16_rn(tot);
+                    }
+                    if (need_kv2 && row_valid) {
+                        float2* rk = (float2*)(ring_k + ring_index<HD>(slot, cbase + c));
+                        float2* rv = (float2*)(ring_v + ring_index<HD>(slot, cbase + c));
+#pragma unroll
+                        for (int e = 0; e < CW / 2; ++e)
+                            rk[e] = __ffma2_rn(make_float2(__uint_as_float(g[2 * e]), __uint_as_float(g[2 * e + 1])),
+                                               make_float2(bf16_lo(qw[e]), bf16_hi(qw[e])), rk[e]);
+#pragma unroll
+                        for (int e = 0; e < CW / 2; ++e)
+                            rv[e] = __ffma2_rn(make_float2(__uint_as_float(u[2 * e]), __uint_as_float(u[2 * e + 1])),
+                                               make_float2(bf16_lo(ow[e]), bf16_hi(ow[e])), rv[e]);
+                    }
+                    named_barrier_sync(3 + grp, 128);
+                }
+                // U / G have been read: the next unit's accumulating MMAs may start
+                tc_fence_before();
+                mbar_arrive(B.acc_free);
+                if (need_kv2 && ring_rows > 0) {
+                    // rows no later query of the run reaches are final: move them to the workspace, clear the slots.
+                    // One row per warp and turn; lanes 0-15 move the group's dK2 columns, lanes 16-31 its dV2 columns.
+                    const bool last_unit = i0 + QPT >= ri.i_run1;
+                    const int f_hi = last_unit ? kb_max + 1 : max(0, i0 + QPT + p.halo2 - (p.w2 - 1));
+                    const bool is_v = lane >= 16;
+                    float* ring = is_v ? ring_v : ring_k;
+                    float* ws_full = is_v ? P.ws_full_v2 : P.ws_full_k2;
+                    float* ws_head = is_v ? P.ws_head_v2 : P.ws_head_k2;
+                    const float mult = is_v ? 1.f : p.scale;                 // the rings hold unscaled sums
+                    for (int kbf = flush_lo + (row >> 5); kbf < f_hi; kbf += 4) {
+                        const int fslot = kbf % ring_rows;
+                        float* dst = (kbf >= own0) ? ws_full + (bh * p.N + (kbf - p.halo2)) * HD
+                                                   : ws_head + ((bh * P.num_runs + ri.run) * (p.w2 - 1) + (kbf - (own0 - (p.w2 - 1)))) * HD;
+                        float* src = ring + ring_index<HD>(fslot, 0);
+                        const int d = cbase + (lane & 15) * 4;
+                        *(float4*)(dst + d) = make_float4(src[d] * mult, src[d + 1] * mult, src[d + 2] * mult, src[d + 3] * mult);
+                        src[d] = 0.f;
+                        src[d + 1] = 0.f;
+                        src[d + 2] = 0.f;
+                        src[d + 3] = 0.f;
+                    }
+                    flush_lo = max(flush_lo, f_hi);
+                    named_barrier_sync(3 + grp, 128);     // cleared slots are visible before the next unit's updates
+                }
+                SA_PROF_ADD(44 + grp, t_epi);
+            }
+        }
+    } else if (warp == 16) {
+        // ---------------------------------------------------------------- MMA issuer
+        reg_dealloc<64>();
+        {
+            const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
+            uint32_t nb[2] = {0, 0}, g_base = 0, n_units = 0;
+            const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false);
+            const uint32_t a_s = smem_base + L::kStat0, c_s = smem_base + L::kStat1;
+            for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
+                const RowItem ri = row_item(P, it);
+                for (int i0 = ri.i_run0; i0 < ri.i_run1; i0 += QPT, ++n_units) {
+                    const RowUnit ru = row_unit(P, i0);
+                    mbar_wait(B.stat_full, n_units & 1, wctx, 32);      // A, C formed
+                    tc_fence_after();
+                    for (int t = 0; t <= ru.nt; ++t) {
+                        if (t < ru.nt) {
+                            const uint32_t g = g_base + t;
+                            const int stage = (int)(g % NS), b = t & 1;
+                            const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
+                            const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
+                            mbar_wait(&B.st_full[stage], (g / NS) & 1, wctx, 33);
+                            tc_fence_after();
+                            issue_sdp<HD>(leader, tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false));
+                            tc_commit(leader, &B.sdp_ready[b]);
+                            if (t == ru.nt - 1) tc_commit(leader, B.stat_empty);     // A and C may be overwritten
+                        }
+                        if (t >= 1) {
+                            const int tp = t - 1;
+                            const uint32_t g = g_base + tp;
+                            const int stage = (int)(g % NS), b = tp & 1;
+                            const int width = (tp == ru.nt - 1) ? ru.last_width : kStreamRows;
+                            const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
+                            mbar_wait(&B.pds_ready[b], nb[b] & 1, wctx, 34);
+                            ++nb[b];
+                            // the previous unit's U and G have been read out by the epilogue groups
+                            if (tp == 0 && n_units > 0) mbar_wait(B.acc_free, (n_units - 1) & 1, wctx, 38);
+                            tc_fence_after();
+                            // U += P V1-tile ; G += dS K1-tile
+                            issue_acc<HD>(leader, tm_u, tm_g, tm_s[b], tm_dp[b], k1_t, v1_t, width / 16, tp > 0);
+                            tc_commit(leader, &B.st_empty[stage]);
+                        }
+                    }
+                    tc_commit(leader, B.acc_ready);
+                    g_base += ru.nt;
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 17) {
+        // ---------------------------------------------------------------- TMA: streamed K1 / V1 tiles
+        reg_dealloc<64>();
+        if (lane == 0) {
+            prefetch_tensormap(&map_k1);
+            prefetch_tensormap(&map_v1);
+            uint32_t g = 0;
+            for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
+                const RowItem ri = row_item(P, it);
+                for (int i0 = ri.i_run0; i0 < ri.i_run1; i0 += QPT) {
+                    const RowUnit ru = row_unit(P, i0);
+                    for (int t = 0; t < ru.nt; ++t, ++g) {
+                        const int stage = (int)(g % NS);
+                        const int r0 = ru.col_start + t * kStreamRows;
+                        uint8_t* k1_t = smem + L::kStream + stage * 2 * L::kSmallTile;
+                        uint8_t* v1_t = k1_t + L::kSmallTile;
+                        mbar_wait(&B.st_empty[stage], ((g / NS) & 1) ^ 1, wctx, 35);
+                        mbar_arrive_expect_tx(&B.st_full[stage], 2 * L::kSmallTile);
+#pragma unroll
+                        for (int sl = 0; sl < L::kSlabs; ++sl) {
+                            tma_load_4d(k1_t + sl * L::kSmallSlab, &map_k1, &B.st_full[stage], sl * 64, r0, ri.hk, ri.b);
+                            tma_load_4d(v1_t + sl * L::kSmallSlab, &map_v1, &B.st_full[stage], sl * 64, r0, ri.hk, ri.b);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        reg_dealloc<64>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    SA_PROF_LIFE(t_life);
+    if (warp == 16) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
 // 4. dK2 / dV2 from the fp32 partials: sum over the query heads of a group, add the head partials of
 //    the runs that start within w2-1 queries after the row, convert to bf16.
 // ------------------------------------------------------------------------------------------------
@@ -1238,14 +1573,14 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         // shared-memory ring of fp32 dK2/dV2 rows beside the tiles: with the 3-stage K1/V1 ring if it fits,
         // else with 2 stages, else none (partials then accumulate in the workspace)
         const int ring_want = (1 << pl.dw_log2) + pl.qpt;
-        auto launch_row = [&](auto kern, int k_ring, int k_min, int max_dyn, int hd) -> bool {
+        auto launch_row = [&](auto kern, int k_ring, int k_min, int max_dyn, int hd, int threads = kRowThreads) -> bool {
             int ring_rows = ring_want;
             int smem = k_ring + 1024 + 2 * ring_rows * (hd + 2) * 4;
             if (!need_kv2 || smem > max_dyn) { ring_rows = 0; smem = k_ring + 1024; }
             if (smem < k_min) smem = k_min;
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn) != cudaSuccess) return false;
-            kern<<<(unsigned)grid, kRowThreads, smem, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o), (__nv_bfloat16*)dq,
-                                                            need_kv2, ring_rows);
+            kern<<<(unsigned)grid, threads, smem, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o), (__nv_bfloat16*)dq,
+                                                        need_kv2, ring_rows);
             return true;
         };
         bool ok;
@@ -1253,7 +1588,10 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
             using L3 = BwdSmem<128, 3>;
             using L2 = BwdSmem<128, 2>;
             const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 130 * 4 <= L3::kMaxDynamic;
-            if (pl.dw_log2 == 4)
+            if (pl.dw_log2 == 5 && (fits3 || !need_kv2))     // separate epilogue warpgroups
+                ok = launch_row(has_bias ? bwd_row2_kernel<128, true> : bwd_row2_kernel<128, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128,
+                                kRow2Threads);
+            else if (pl.dw_log2 == 4)
                 ok = launch_row(has_bias ? bwd_row_kernel<128, 3, true, true> : bwd_row_kernel<128, 3, true, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128);
             else
                 ok = (fits3 || !need_kv2) ? launch_row(has_bias ? bwd_row_kernel<128, 3, false, true> : bwd_row_kernel<128, 3, false, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128)
