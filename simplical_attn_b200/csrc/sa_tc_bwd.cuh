@@ -13,22 +13,24 @@
 //
 // Three launches plus a tiny one:
 //   1. prep_kernel      Delta_i = dO_i . O_i and LSE2_i = LSE_i * log2e                (fp32)
-//   2. bwd_col_kernel   a block owns 128 K1/V1 rows of one KV head, streams 64-row tiles of A and C
-//                       (formed on chip) for every query head of the group, accumulates dV1 and
-//                       dK1 in tensor memory and writes them once.
-//   3. bwd_row_kernel   a block owns a run of consecutive queries of one query head; per 128-row
+//   2. bwd_col_kernel   a block owns 128 K1/V1 rows of one KV head, streams 128-row tiles of A and C
+//                       (formed on chip by two producer warpgroups) for every query head of the
+//                       group, accumulates dV1 and dK1 in tensor memory and writes them once.
+//   3. bwd_row_kernel / bwd_row2_kernel
+//                       a block owns a run of consecutive queries of one query head; per 128-row
 //                       tile it streams 64-row K1/V1 tiles by TMA, accumulates U and G in tensor
 //                       memory, merges G over delta into dQ and adds the per-K2-row sums of G*Q and
 //                       U*dO into fp32 partial buffers in the workspace (plain read-modify-write:
-//                       a row is only ever touched by one block, in program order).
+//                       a row is only ever touched by one block, in program order).  The second
+//                       form has separate epilogue warpgroups (32 delta slots per query, D = 128).
 //   4. kv2_reduce_kernel sums those partials over the query heads of a group and over run
 //                       boundaries and writes dK2, dV2.
 //
-// Both big kernels share one pipeline: S and dP tiles (128 lanes x 64 columns) are double buffered
-// in tensor memory; softmax group b (4 warps) turns buffer b into P and dS (bf16, in place) while the
-// tensor cores work on the other buffer; P and dS then feed the two accumulating MMAs from tensor
-// memory.  Warps 0-3 / 4-7: softmax groups (in the column kernel they also form the streamed A / C
-// tiles, four tiles ahead of their use), warp 8: MMA issuer, warp 9: TMA issuer.
+// Row kernels: S and dP tiles (128 lanes x 64 columns) are double buffered in tensor memory; softmax
+// group b (4 warps) turns buffer b into P and dS (bf16, in place) while the tensor cores work on the
+// other buffer; P and dS then feed the two accumulating MMAs from tensor memory.  Column kernel: one
+// 128-column S^T / dP^T pair, both softmax groups split its columns and hand P^T / dS^T to the MMA
+// warp in 16-column chunks.  Every kernel has one MMA-issuing warp and one TMA-issuing warp.
 #pragma once
 
 #include <type_traits>
