@@ -1151,7 +1151,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
     const uint32_t tm_dp[2] = {tmem_base + 128, tmem_base + 192};
     const uint32_t tm_u = tmem_base + 256, tm_g = tmem_base + 384;     // U = P V1, G = dS K1
 
-    // Register pool of the block: 640 x 96 = 2 x 120 (softmax groups) + 2 x 88 (epilogue groups) + 64 (the
+    // Register pool of the block: 640 x 96 = 2 x 120 (softmax groups) + 2 x 96 (epilogue groups) + 48 (the
     // rest): an increase beyond the block's own pool would never return.
     if (warp < 8) {
         // ---------------------------------------------------------------- operand formation + softmax
@@ -1224,7 +1224,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         // ---------------------------------------------------------------- epilogue groups: group g takes columns
         // [g * HD/2, (g + 1) * HD/2) of all three results (dQ and dK2 from G, dV2 from U), so both groups
         // carry the same load and no ring column is shared between them
-        reg_dealloc<88>();
+        // (these groups keep the 96 registers the block was launched with)
         const int grp = (warp - 8) >> 2;
         const int row = tid & 127;
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
@@ -1340,7 +1340,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         }
     } else if (warp == 16) {
         // ---------------------------------------------------------------- MMA issuer
-        reg_dealloc<64>();
+        reg_dealloc<48>();
         {
             const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
             uint32_t nb[2] = {0, 0}, g_base = 0, n_units = 0;
@@ -1388,7 +1388,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         __syncwarp();
     } else if (warp == 17) {
         // ---------------------------------------------------------------- TMA: streamed K1 / V1 tiles
-        reg_dealloc<64>();
+        reg_dealloc<48>();
         if (lane == 0) {
             prefetch_tensormap(&map_k1);
             prefetch_tensormap(&map_v1);
@@ -1415,7 +1415,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         }
         __syncwarp();
     } else {
-        reg_dealloc<64>();
+        reg_dealloc<48>();
     }
     tc_fence_before();
     __syncthreads();
