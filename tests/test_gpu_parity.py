@@ -239,6 +239,26 @@ def test_window_sweep_tensor_core_vs_general(w1, w2):
         assert so.rel_l2(a.float().cpu(), b.float().cpu()) <= TOL_G_BF16, nm
 
 
+@pytest.mark.parametrize("w2", [16, 32, 64])
+def test_partial_gradient_requests_match_full_call(w2):
+    """The reference's two backward kernels are separate calls (dQ/dK1/dV1 and dK2/dV2).  Asking the
+    tensor-core path for a subset must give exactly the tensors of the full call (w2 = 32 runs the row
+    kernel with separate epilogue warpgroups, 16 and 64 the other one) and None for the rest."""
+    B, N, H, Hkv, D, w1 = 1, 700, 4, 2, 128, 200
+    q, k1, k2, v1, v2, do = so.make_inputs(B, N, H, Hkv, D, seed=11 + w2)
+    cfg = dict(w1=w1, w2=w2, scale=1.0 / math.sqrt(D), k2_bias=0.0, v2_bias=0.0)
+    ins = dict(q=q, k1=k1, k2=k2, v1=v1, v2=v2, do=do)
+    _, _, full = _run(ins, cfg, "tcgen05")
+    for need in ((True, True, False, True, False), (False, False, True, False, True), (True, False, False, False, False),
+                 (False, False, False, False, True)):
+        _, _, part = _run(ins, cfg, "tcgen05", need=need)
+        for nm, n, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), need, part, full):
+            if n:
+                assert torch.equal(a, b), (nm, need)
+            else:
+                assert a is None, (nm, need)
+
+
 def test_grouped_heads_full_size():
     """The grouped-head configuration (B1, 32 query heads on 2 KV heads, N=16384, D=128, w 512/32): forward
     row slices against the C loop oracle, all five gradients against the general kernels (which sum
