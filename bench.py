@@ -227,7 +227,7 @@ def main():
 
     host_out = [torch.empty_like(h).pin_memory() for h in (host[0], host[0], host[1], host[2], host[3], host[4])]
     from simplical_attn_b200.host_pipeline import HostPipeline
-    pipe = HostPipeline(device, chunk=2)
+    pipe = HostPipeline(device)
 
     def step_e2e():
         # the library's host-tensor entry point: pinned host inputs in, pinned host results out; the

@@ -20,7 +20,10 @@ from . import simplicial_attn as _op
 class HostPipeline:
     """Reusable buffers and streams for repeated host-to-host forward+backward calls of one shape."""
 
-    def __init__(self, device, chunk: int = 2):
+    def __init__(self, device, chunk: int = 1):
+        # chunk = sequences per pipeline stage.  The first upload and the last download are not hidden
+        # by compute, so small chunks win as long as one chunk fills the GPU: at B16 H16 N8192 D128
+        # one sequence per chunk measured 129.5 ms per call, two 135.8 ms, four 148.7 ms.
         self.device = torch.device(device)
         self.chunk = int(chunk)
         self.s_in = torch.cuda.Stream(self.device)
