@@ -1092,7 +1092,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 }
 
 // ------------------------------------------------------------------------------------------------
-// 3b. Row kernel with separate epilogue warpgroups, for 32 delta slots per query (w2 in 17..32) when
+// 3b. Row kernel with separate epilogue warpgroups, for 16 or 32 delta slots per query (w2 in 9..32) when
 //     the dK2/dV2 ring fits: warps 0-7 form the operands and run the softmax, warps 8-15 read U and G
 //     out of tensor memory (dQ, dK2 ring, dV2 ring) while warps 0-7 already work on the next unit, so
 //     the epilogue of a unit overlaps the main loop of the next one.  Same math, same order of
@@ -1100,7 +1100,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 // ------------------------------------------------------------------------------------------------
 constexpr int kRow2Threads = 640;     // softmax groups (0-7), epilogue groups (8-15), MMA (16), TMA (17), 2 idle
 
-template <int HD, bool BIAS>
+template <int HD, int DWL, bool BIAS>
 __global__ void __launch_bounds__(kRow2Threads, 1)
 bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
                 const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
@@ -1111,7 +1111,9 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
     using namespace ptx;
     constexpr int CW = 16;                                // epilogue chunk width
     constexpr int NPH = HD / CW;                          // epilogue phases
-    constexpr int DWL = 5, DW = 32, QPT = 4;              // delta slots per query, queries per 128-row unit
+    static_assert(DWL == 4 || DWL == 5, "16 or 32 delta slots per query");
+    constexpr int DW = 1 << DWL, QPT = 128 >> DWL;        // delta slots per query, queries per 128-row unit
+    constexpr bool TWO_Q = DWL == 4;                      // a warp holds two queries of 16 deltas each
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
@@ -1230,7 +1232,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
         const int qq = row >> DWL;
         const int dlt = row & (DW - 1);
-        const int wq = row >> 5;                          // warp within the group = query within the unit
+        const int wq = row >> 5;                          // warp within the group
         constexpr int HALF = HD / 2;
         constexpr int NPHG = HALF / CW;                   // phases per group (4 at HD = 128)
         static_assert(NPHG == 4, "one column chunk per warp and phase");
@@ -1266,7 +1268,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                 mbar_wait(B.acc_ready, n_units & 1, wctx, 31);
                 tc_fence_after();
                 SA_PROF_T0(t_epi);
-                // A warp holds the 32 deltas of one query: within it the lanes own distinct K2 rows.  Warp w works
+                // A warp holds the 32 deltas of one query (or the 16 deltas of two): within a query the lanes own distinct K2 rows.  Warp w works
                 // on column chunk (w + phase) % 4 of the group's half, so no two warps touch the same ring columns
                 // at the same time; the delta sum for dQ is a register exchange inside the warp.  Rows that are
                 // not valid have P = dS = 0, hence exact zeros in U and G: they need no masking in the sums.
@@ -1290,20 +1292,33 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                             v[e] = t.x;
                             v[e + 1] = t.y;
                         }
-                        const float tot = warp_transpose_reduce<CW>(v, lane) * p.scale;
-                        if (lane < CW && i0 + wq < p.N) dq_out[(long)wq * p.dq.n + c + lane] = __float2bfloat16_rn(tot);
+                        if constexpr (!TWO_Q) {
+                            const float tot = warp_transpose_reduce<CW>(v, lane) * p.scale;
+                            if (lane < CW && i0 + wq < p.N) dq_out[(long)wq * p.dq.n + c + lane] = __float2bfloat16_rn(tot);
+                        } else {
+                            // each half warp holds the 16 deltas of one query
+                            const int qh = wq * 2 + (lane >> 4);
+                            const float tot = half_warp_transpose_reduce16(v, lane) * p.scale;
+                            if (i0 + qh < p.N) dq_out[(long)qh * p.dq.n + c + (lane & 15)] = __float2bfloat16_rn(tot);
+                        }
                     }
-                    if (need_kv2 && row_valid) {
-                        float2* rk = (float2*)(ring_k + ring_index<HD>(slot, cbase + c));
-                        float2* rv = (float2*)(ring_v + ring_index<HD>(slot, cbase + c));
+                    // With two queries in a warp, lanes (q, delta) and (q + 1, delta + 1) own the same K2 row: the
+                    // halves take turns.
 #pragma unroll
-                        for (int e = 0; e < CW / 2; ++e)
-                            rk[e] = __ffma2_rn(make_float2(__uint_as_float(g[2 * e]), __uint_as_float(g[2 * e + 1])),
-                                               make_float2(bf16_lo(qw[e]), bf16_hi(qw[e])), rk[e]);
+                    for (int turn = 0; turn < (TWO_Q ? 2 : 1); ++turn) {
+                        if (need_kv2 && row_valid && (!TWO_Q || (lane >> 4) == turn)) {
+                            float2* rk = (float2*)(ring_k + ring_index<HD>(slot, cbase + c));
+                            float2* rv = (float2*)(ring_v + ring_index<HD>(slot, cbase + c));
 #pragma unroll
-                        for (int e = 0; e < CW / 2; ++e)
-                            rv[e] = __ffma2_rn(make_float2(__uint_as_float(u[2 * e]), __uint_as_float(u[2 * e + 1])),
-                                               make_float2(bf16_lo(ow[e]), bf16_hi(ow[e])), rv[e]);
+                            for (int e = 0; e < CW / 2; ++e)
+                                rk[e] = __ffma2_rn(make_float2(__uint_as_float(g[2 * e]), __uint_as_float(g[2 * e + 1])),
+                                                   make_float2(bf16_lo(qw[e]), bf16_hi(qw[e])), rk[e]);
+#pragma unroll
+                            for (int e = 0; e < CW / 2; ++e)
+                                rv[e] = __ffma2_rn(make_float2(__uint_as_float(u[2 * e]), __uint_as_float(u[2 * e + 1])),
+                                                   make_float2(bf16_lo(ow[e]), bf16_hi(ow[e])), rv[e]);
+                        }
+                        if (TWO_Q) __syncwarp();
                     }
                     named_barrier_sync(3 + grp, 128);
                 }
@@ -1591,8 +1606,11 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
             using L2 = BwdSmem<128, 2>;
             const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 130 * 4 <= L3::kMaxDynamic;
             if (pl.dw_log2 == 5 && (fits3 || !need_kv2))     // separate epilogue warpgroups
-                ok = launch_row(has_bias ? bwd_row2_kernel<128, true> : bwd_row2_kernel<128, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128,
-                                kRow2Threads);
+                ok = launch_row(has_bias ? bwd_row2_kernel<128, 5, true> : bwd_row2_kernel<128, 5, false>, L3::kRing, L3::kAlloc,
+                                L3::kMaxDynamic, 128, kRow2Threads);
+            else if (pl.dw_log2 == 4 && (fits3 || !need_kv2))
+                ok = launch_row(has_bias ? bwd_row2_kernel<128, 4, true> : bwd_row2_kernel<128, 4, false>, L3::kRing, L3::kAlloc,
+                                L3::kMaxDynamic, 128, kRow2Threads);
             else if (pl.dw_log2 == 4)
                 ok = launch_row(has_bias ? bwd_row_kernel<128, 3, true, true> : bwd_row_kernel<128, 3, true, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128);
             else
