@@ -1092,7 +1092,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 }
 
 // ------------------------------------------------------------------------------------------------
-// 3b. Row kernel with separate epilogue warpgroups, for 16 or 32 delta slots per query (w2 in 9..32) when
+// 3b. Row kernel with separate epilogue warpgroups, for 16, 32 or 64 delta slots per query (w2 in 9..64) when
 //     the dK2/dV2 ring fits: warps 0-7 form the operands and run the softmax, warps 8-15 read U and G
 //     out of tensor memory (dQ, dK2 ring, dV2 ring) while warps 0-7 already work on the next unit, so
 //     the epilogue of a unit overlaps the main loop of the next one.  Same math, same order of
@@ -1100,20 +1100,20 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 // ------------------------------------------------------------------------------------------------
 constexpr int kRow2Threads = 640;     // softmax groups (0-7), epilogue groups (8-15), MMA (16), TMA (17), 2 idle
 
-template <int HD, int DWL, bool BIAS>
+template <int HD, int DWL, int NS, bool BIAS>
 __global__ void __launch_bounds__(kRow2Threads, 1)
 bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
                 const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
                 const __nv_bfloat16* __restrict__ k2, const __nv_bfloat16* __restrict__ v2,
                 const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dq, int need_kv2, int ring_rows) {
-    constexpr int NS = kRowStages;
     using L = BwdSmem<HD, NS>;
     using namespace ptx;
     constexpr int CW = 16;                                // epilogue chunk width
     constexpr int NPH = HD / CW;                          // epilogue phases
-    static_assert(DWL == 4 || DWL == 5, "16 or 32 delta slots per query");
+    static_assert(DWL >= 4 && DWL <= 6, "16, 32 or 64 delta slots per query");
     constexpr int DW = 1 << DWL, QPT = 128 >> DWL;        // delta slots per query, queries per 128-row unit
     constexpr bool TWO_Q = DWL == 4;                      // a warp holds two queries of 16 deltas each
+    constexpr int WPQ = DW > 32 ? DW / 32 : 1;            // warps per query
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
@@ -1241,6 +1241,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         // per row modulo ring_rows
         float* ring_k = (float*)(smem + L::kRing);
         float* ring_v = ring_k + ring_rows * (HD + 2);
+        float* dq_part = ring_v + ring_rows * (HD + 2) + grp * 4 * HALF;     // [4 warps][HALF] when a query spans two warps
         for (int x = row; x < ring_rows * HALF; x += 128) {
             const int idx = ring_index<HD>(x / HALF, cbase + x % HALF);
             ring_k[idx] = 0.f;
@@ -1294,7 +1295,11 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                         }
                         if constexpr (!TWO_Q) {
                             const float tot = warp_transpose_reduce<CW>(v, lane) * p.scale;
-                            if (lane < CW && i0 + wq < p.N) dq_out[(long)wq * p.dq.n + c + lane] = __float2bfloat16_rn(tot);
+                            if (WPQ == 1) {
+                                if (lane < CW && i0 + wq < p.N) dq_out[(long)wq * p.dq.n + c + lane] = __float2bfloat16_rn(tot);
+                            } else if (lane < CW) {
+                                dq_part[wq * HALF + c + lane] = tot;
+                            }
                         } else {
                             // each half warp holds the 16 deltas of one query
                             const int qh = wq * 2 + (lane >> 4);
@@ -1325,6 +1330,17 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                 // U / G have been read: the next unit's accumulating MMAs may start
                 tc_fence_before();
                 mbar_arrive(B.acc_free);
+                if (WPQ > 1 && dq != nullptr) {
+                    // a query spans WPQ warps: add their partial rows (the last phase ended with a barrier)
+                    for (int idx = row; idx < QPT * HALF; idx += 128) {
+                        const int q2 = idx / HALF, col = idx % HALF;
+                        float a = 0.f;
+#pragma unroll
+                        for (int w = 0; w < WPQ; ++w) a += dq_part[(q2 * WPQ + w) * HALF + col];
+                        if (i0 + q2 < p.N) dq_out[(long)q2 * p.dq.n + col] = __float2bfloat16_rn(a);
+                    }
+                    named_barrier_sync(3 + grp, 128);     // before the next unit overwrites the partial rows
+                }
                 if (need_kv2 && ring_rows > 0) {
                     // rows no later query of the run reaches are final: move them to the workspace, clear the slots.
                     // One row per warp and turn; lanes 0-15 move the group's dK2 columns, lanes 16-31 its dV2 columns.
@@ -1590,10 +1606,10 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
         // shared-memory ring of fp32 dK2/dV2 rows beside the tiles: with the 3-stage K1/V1 ring if it fits,
         // else with 2 stages, else none (partials then accumulate in the workspace)
         const int ring_want = (1 << pl.dw_log2) + pl.qpt;
-        auto launch_row = [&](auto kern, int k_ring, int k_min, int max_dyn, int hd, int threads = kRowThreads) -> bool {
+        auto launch_row = [&](auto kern, int k_ring, int k_min, int max_dyn, int hd, int threads = kRowThreads, int extra = 0) -> bool {
             int ring_rows = ring_want;
-            int smem = k_ring + 1024 + 2 * ring_rows * (hd + 2) * 4;
-            if (!need_kv2 || smem > max_dyn) { ring_rows = 0; smem = k_ring + 1024; }
+            int smem = k_ring + 1024 + 2 * ring_rows * (hd + 2) * 4 + extra;
+            if (!need_kv2 || smem > max_dyn) { ring_rows = 0; smem = k_ring + 1024 + extra; }
             if (smem < k_min) smem = k_min;
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, max_dyn) != cudaSuccess) return false;
             kern<<<(unsigned)grid, threads, smem, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o), (__nv_bfloat16*)dq,
@@ -1605,12 +1621,21 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
             using L3 = BwdSmem<128, 3>;
             using L2 = BwdSmem<128, 2>;
             const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 130 * 4 <= L3::kMaxDynamic;
-            if (pl.dw_log2 == 5 && (fits3 || !need_kv2))     // separate epilogue warpgroups
-                ok = launch_row(has_bias ? bwd_row2_kernel<128, 5, true> : bwd_row2_kernel<128, 5, false>, L3::kRing, L3::kAlloc,
-                                L3::kMaxDynamic, 128, kRow2Threads);
-            else if (pl.dw_log2 == 4 && (fits3 || !need_kv2))
-                ok = launch_row(has_bias ? bwd_row2_kernel<128, 4, true> : bwd_row2_kernel<128, 4, false>, L3::kRing, L3::kAlloc,
-                                L3::kMaxDynamic, 128, kRow2Threads);
+            constexpr int kDqPart = 2048;     // partial dQ rows of the epilogue groups when a query spans two warps
+            const bool fits2 = L2::kRing + 1024 + 2 * ring_want * 130 * 4 + kDqPart <= L2::kMaxDynamic;
+            const bool fits3x = L3::kRing + 1024 + 2 * ring_want * 130 * 4 + kDqPart <= L3::kMaxDynamic;
+            if (pl.dw_log2 == 5 && (fits3x || !need_kv2))     // separate epilogue warpgroups
+                ok = launch_row(has_bias ? bwd_row2_kernel<128, 5, 3, true> : bwd_row2_kernel<128, 5, 3, false>, L3::kRing, L3::kAlloc,
+                                L3::kMaxDynamic, 128, kRow2Threads, kDqPart);
+            else if (pl.dw_log2 == 4 && (fits3x || !need_kv2))
+                ok = launch_row(has_bias ? bwd_row2_kernel<128, 4, 3, true> : bwd_row2_kernel<128, 4, 3, false>, L3::kRing, L3::kAlloc,
+                                L3::kMaxDynamic, 128, kRow2Threads, kDqPart);
+            else if (pl.dw_log2 == 6 && (fits3x || !need_kv2))
+                ok = launch_row(has_bias ? bwd_row2_kernel<128, 6, 3, true> : bwd_row2_kernel<128, 6, 3, false>, L3::kRing, L3::kAlloc,
+                                L3::kMaxDynamic, 128, kRow2Threads, kDqPart);
+            else if (pl.dw_log2 == 6 && fits2)
+                ok = launch_row(has_bias ? bwd_row2_kernel<128, 6, 2, true> : bwd_row2_kernel<128, 6, 2, false>, L2::kRing, L2::kAlloc,
+                                L2::kMaxDynamic, 128, kRow2Threads, kDqPart);
             else if (pl.dw_log2 == 4)
                 ok = launch_row(has_bias ? bwd_row_kernel<128, 3, true, true> : bwd_row_kernel<128, 3, true, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128);
             else
