@@ -326,9 +326,9 @@ def main():
         # (G, U and the other half).  DRAM traffic per launch comes from the ncu capture of a one-batch
         # case (profiles/), scaled by the rank's batch: traffic grows in proportion to the batch.
         kernels = {
-            "fwd_tc_kernel": (ms_fwd, 2.0 * unit_rank, 194.2e6 * Bl),
-            "bwd_col_kernel": (ms_col, 3.0 * unit_rank, 246.6e6 * Bl),
-            "bwd_row_kernel": (ms_row, 3.0 * unit_rank, 396.8e6 * Bl),
+            "fwd_tc_kernel": (ms_fwd, 2.0 * unit_rank, 194.6e6 * Bl),
+            "bwd_col_kernel": (ms_col, 3.0 * unit_rank, 247.0e6 * Bl),
+            "bwd_row_kernel": (ms_row, 3.0 * unit_rank, 395.0e6 * Bl),
         }
         dom = max(kernels, key=lambda k: kernels[k][0])
         dom_ms, dom_fl, dom_traffic = kernels[dom]
