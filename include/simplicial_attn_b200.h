@@ -79,22 +79,32 @@ int sa_backward(const sa_params* p, const void* q, const void* k1, const void* k
                 const void* v2, const void* o, const float* lse, const void* d_o, void* dq, void* dk1,
                 void* dk2, void* dv1, void* dv2, void* workspace, size_t workspace_bytes, void* stream);
 
-/* The same backward for callers that cannot allocate device memory -- code running inside a stream
- * capture or a graph replay, inside a framework's allocator callback, or in a process whose memory
- * pool is owned and fully handed out by someone else, where a cudaMalloc would fail, deadlock or
- * break the capture.  It has no counterpart in the reference.  Instead of a caller workspace it uses
- * a 32 MiB scratch array built into the library image (so every GPU that loads the library gives
- * up that much memory until the process exits) and calls no cudaMalloc, cudaFree or other
- * allocating routine.  Problems whose sa_backward_workspace_size() exceeds
- * sa_backward_static_capacity() are rejected with SA_ERR_WORKSPACE.  The first call on each device
- * looks the array's device address up (with that device current); make that call before any stream
- * capture begins.  All calls on a device share the one array: two calls whose kernels may overlap
- * on the GPU (different streams, no ordering between them) race on it, so keep them ordered.  The
- * device status word is cleared at the start of every call. */
+/* The same backward for callers that have no way to obtain a device workspace at the moment they
+ * need the gradients.  Typical cases: a plugin that runs inside a host framework's memory-allocator
+ * callback, where calling the allocator again would re-enter it or deadlock; a worker in a process
+ * whose device memory was handed out in full to a pool that somebody else owns, so that a cudaMalloc
+ * fails; a real-time loop that is not allowed to take the allocation lock at all.  It has no
+ * counterpart in the reference.  Instead of a caller workspace the call uses a 32 MiB scratch array
+ * that is part of the library image -- every GPU that loads the library gives up that much memory
+ * until the process exits -- and it calls no cudaMalloc, cudaFree or any other allocating routine.
+ * Problems whose sa_backward_workspace_size() exceeds sa_backward_static_capacity() are rejected
+ * with SA_ERR_WORKSPACE (at D=128, w2=32 the limit is about 30 000 query rows summed over batch and
+ * heads).  The first call on each device looks up the array's device address, with that device
+ * current; make that first call before any stream capture begins.  All calls on a device share the
+ * one array and find in it whatever the previous call left: two calls whose kernels may overlap on
+ * the GPU (different streams with no ordering between them) race on it, so keep them ordered.
+ * The array's first bytes hold the device status word.  It is zero when the library is loaded and
+ * the call does not clear it, so a timeout recorded by an earlier call stays visible until
+ * sa_read_status_static() reports and clears it. */
 int sa_backward_static(const sa_params* p, const void* q, const void* k1, const void* k2, const void* v1,
                        const void* v2, const void* o, const float* lse, const void* d_o, void* dq, void* dk1,
                        void* dk2, void* dv1, void* dv2, void* stream);
 size_t sa_backward_static_capacity(void);
+
+/* sa_read_status() for the built-in scratch array of sa_backward_static(): synchronises `stream`,
+ * returns SA_OK or SA_ERR_DEVICE_TIMEOUT and clears the word.  Call it after the calls whose result
+ * you are about to trust.  No counterpart in the reference. */
+int sa_read_status_static(void* stream);
 
 /* Workspace sizes in bytes for the given problem (the reference allocates its work buffers inside
  * the autograd function, triton_impl.py:23-25,73-77; here the caller does).  Never 0: the first
@@ -106,6 +116,23 @@ size_t sa_backward_workspace_size(const sa_params* p);
  * `workspace` (SA_OK or SA_ERR_DEVICE_TIMEOUT), then clears it.  The reference has no
  * counterpart: its failures surface as Triton exceptions. */
 int sa_read_status(void* workspace, void* stream);
+
+/* The same, also returning where the wait gave up: `where` receives the id of the wait site inside
+ * the kernel and `block` the index of the thread block that recorded it (either may be NULL). */
+int sa_read_status_ex(void* workspace, void* stream, int* where, int* block);
+
+/* Every wait inside the kernels (on an mbarrier that another warp, the TMA unit or the tensor cores
+ * complete) is bounded: when it lasts longer than the limit the block records
+ * SA_ERR_DEVICE_TIMEOUT in the status word, stops waiting and returns, so the context stays usable.
+ * The limit is 2 s unless changed here (0 restores the default); it applies to calls made afterwards,
+ * process-wide.  No counterpart in the reference. */
+void sa_set_wait_limit_ns(uint64_t limit_ns);
+
+/* Self-test of that mechanism: launches one warp that waits, with the given limit (at most 0.1 s),
+ * on a barrier nobody arrives on.  The kernel returns by itself once the limit has passed; afterwards
+ * sa_read_status(workspace) reports SA_ERR_DEVICE_TIMEOUT.  `workspace` needs 256 bytes, 256-byte
+ * aligned, zero status word.  Nothing faults, traps or spins without a bound. */
+int sa_selftest_wait_timeout(void* workspace, uint64_t limit_ns, void* stream);
 
 /* Which kernel family AUTO resolves to for `p` (SA_ALGO_GENERAL or SA_ALGO_TCGEN05), or a negative
  * sa_status if `p` is invalid. */

@@ -17,7 +17,8 @@ SA_ALGO_AUTO, SA_ALGO_GENERAL, SA_ALGO_TCGEN05 = 0, 1, 2
 
 EXPORTS = ("sa_forward", "sa_backward", "sa_forward_workspace_size", "sa_backward_workspace_size", "sa_read_status",
            "sa_resolve_algo", "sa_strerror", "sa_version", "sa_kernel_launches", "sa_backward_static",
-           "sa_backward_static_capacity")
+           "sa_backward_static_capacity", "sa_read_status_static", "sa_read_status_ex", "sa_set_wait_limit_ns",
+           "sa_selftest_wait_timeout")
 
 
 class Strides(ctypes.Structure):
@@ -49,8 +50,10 @@ def load():
     if _lib is not None:
         return _lib
     path = _build.LIB
-    if not os.path.exists(path):
-        path = _build.build()
+    if _build.have_compiler():
+        path = _build.build()              # returns at once unless a source is newer than the library
+    elif not os.path.exists(path):
+        raise OSError(f"{path} is missing and there is no nvcc to build it")
     lib = ctypes.CDLL(path)
     vp, sz = ctypes.c_void_p, ctypes.c_size_t
     pp = ctypes.POINTER(Params)
@@ -67,6 +70,14 @@ def load():
     lib.sa_backward_workspace_size.restype = sz
     lib.sa_read_status.argtypes = [vp, vp]
     lib.sa_read_status.restype = ctypes.c_int
+    lib.sa_read_status_ex.argtypes = [vp, vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
+    lib.sa_read_status_ex.restype = ctypes.c_int
+    lib.sa_read_status_static.argtypes = [vp]
+    lib.sa_read_status_static.restype = ctypes.c_int
+    lib.sa_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
+    lib.sa_set_wait_limit_ns.restype = None
+    lib.sa_selftest_wait_timeout.argtypes = [vp, ctypes.c_uint64, vp]
+    lib.sa_selftest_wait_timeout.restype = ctypes.c_int
     lib.sa_resolve_algo.argtypes = [pp]
     lib.sa_resolve_algo.restype = ctypes.c_int
     lib.sa_strerror.argtypes = [ctypes.c_int]

@@ -19,6 +19,14 @@ NVCC_FLAGS = [
 ]
 
 
+def nvcc_path() -> str:
+    return os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+
+
+def have_compiler() -> bool:
+    return os.path.exists(nvcc_path())
+
+
 def sources():
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
 
@@ -36,7 +44,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     """Compile the library if it is missing or older than its sources; returns its path."""
     if not force and not _stale():
         return LIB
-    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    nvcc = nvcc_path()
     os.makedirs(LIB_DIR, exist_ok=True)
     cmd = [nvcc] + NVCC_FLAGS + ["-o", LIB] + sources()
     res = subprocess.run(cmd, capture_output=True, text=True)

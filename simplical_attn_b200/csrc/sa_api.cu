@@ -19,6 +19,7 @@ using sa::KParams;
 constexpr size_t kStatusBytes = 256;
 
 std::atomic<uint64_t> g_launches{0};      // kernels launched by this library in this process
+std::atomic<uint64_t> g_wait_limit_ns{sa::ptx::kWaitLimitNs};   // bound of every device-side wait (sa_set_wait_limit_ns)
 
 // Scratch of sa_backward_static: lives in the module image, so every GPU that loads the library
 // carries these bytes until the process exits.  In host code the symbol is only a handle; the
@@ -108,6 +109,23 @@ bool make_map(CUtensorMap* map, const void* base, int B, int rows, int heads, in
     return r == CUDA_SUCCESS;
 }
 
+// Self-test of the bounded wait: one warp waits on an mbarrier that nobody ever arrives on.  The wait
+// gives up after `limit_ns`, records SA_ERR_DEVICE_TIMEOUT in the status word and the kernel returns
+// by itself: nothing traps, nothing spins without a bound.
+__global__ void __launch_bounds__(32) wait_timeout_probe_kernel(sa::DeviceStatus* status, uint64_t limit_ns, int where) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        sa::ptx::mbar_init(&bar, 1);
+        abort_flag = 0;
+        sa::ptx::fence_mbar_init();
+    }
+    __syncwarp();
+    const sa::ptx::WaitCtx ctx{&abort_flag, status, limit_ns};
+    sa::ptx::mbar_wait(&bar, 0, ctx, where);      // phase 0 never completes
+    sa::ptx::mbar_wait(&bar, 0, ctx, where + 1);  // after the first wait gave up every later wait falls through
+}
+
 struct DeviceInfo {
     int sm_count = 0;
     int cc_major = 0;
@@ -144,6 +162,13 @@ void* static_scratch() {
     return slot;
 }
 
+// Multiprocessor count the backward plan is sized for: the current device's, or a B200's when no
+// device is available (size queries on a machine without a GPU).
+int plan_sm_count() {
+    const int n = device_info().sm_count;
+    return n > 0 ? n : 148;
+}
+
 template <typename Kern>
 bool set_smem(Kern kern, int bytes) {
     return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
@@ -163,6 +188,7 @@ int launch_fwd_tc(const sa_params* p, const KParams& k, const void* q, const voi
     P.num_qblocks = (k.N + qpb - 1) / qpb;
     P.num_units = (long)k.B * k.H * P.num_qblocks;
     P.status = reinterpret_cast<sa::DeviceStatus*>(workspace);
+    P.wait_limit_ns = g_wait_limit_ns.load();
     const long grid = P.num_units < dev.sm_count ? P.num_units : dev.sm_count;
     if (k.D == 128) {
         using L = sa::tc::FwdSmem<128>;
@@ -243,17 +269,39 @@ size_t sa_forward_workspace_size(const sa_params* p) {
 size_t sa_backward_workspace_size(const sa_params* p) {
     if (validate(p) != SA_OK) return kStatusBytes;
     if (resolve(p, true) != SA_ALGO_TCGEN05) return kStatusBytes;
-    return kStatusBytes + sa::tc::bwd_workspace_bytes(make_kparams(p));
+    return kStatusBytes + sa::tc::bwd_workspace_bytes(make_kparams(p), plan_sm_count());
 }
 
-int sa_read_status(void* workspace, void* stream) {
+int sa_read_status_ex(void* workspace, void* stream, int* where, int* block) {
     if (!workspace) return SA_ERR_NULL_POINTER;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     sa::DeviceStatus h{};
     if (cudaMemcpyAsync(&h, workspace, sizeof(h), cudaMemcpyDeviceToHost, st) != cudaSuccess) return SA_ERR_LAUNCH;
     if (cudaStreamSynchronize(st) != cudaSuccess) return SA_ERR_LAUNCH;
     if (h.code != 0) cudaMemsetAsync(workspace, 0, sizeof(h), st);
+    if (where) *where = h.where;
+    if (block) *block = h.block;
     return h.code;
+}
+
+int sa_read_status(void* workspace, void* stream) { return sa_read_status_ex(workspace, stream, nullptr, nullptr); }
+
+int sa_read_status_static(void* stream) {
+    void* scratch = static_scratch();
+    if (!scratch) return SA_ERR_LAUNCH;
+    return sa_read_status_ex(scratch, stream, nullptr, nullptr);
+}
+
+void sa_set_wait_limit_ns(uint64_t limit_ns) { g_wait_limit_ns.store(limit_ns ? limit_ns : sa::ptx::kWaitLimitNs); }
+
+int sa_selftest_wait_timeout(void* workspace, uint64_t limit_ns, void* stream) {
+    if (!workspace) return SA_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(workspace) & 255u) return SA_ERR_WORKSPACE;
+    if (limit_ns == 0 || limit_ns > 100000000ull) return SA_ERR_UNSUPPORTED;      // at most 0.1 s for a test
+    wait_timeout_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<sa::DeviceStatus*>(workspace), limit_ns, 90);
+    g_launches += 1;
+    return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
 }
 
 int sa_forward(const sa_params* p, const void* q, const void* k1, const void* k2, const void* v1, const void* v2, void* o,
@@ -304,7 +352,7 @@ int sa_backward(const sa_params* p, const void* q, const void* k1, const void* k
         const int rc = sa::tc::launch_bwd(k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2,
                                           static_cast<uint8_t*>(workspace) + kStatusBytes,
                                           reinterpret_cast<sa::DeviceStatus*>(workspace), st, &nlaunch, &make_map,
-                                          device_info().sm_count);
+                                          plan_sm_count(), g_wait_limit_ns.load());
         g_launches += nlaunch;
         if (rc != -1) return rc;      // -1: the tensor-core backward declines this problem
         if (p->algo == SA_ALGO_TCGEN05) return SA_ERR_UNSUPPORTED;
@@ -325,8 +373,10 @@ int sa_backward_static(const sa_params* p, const void* q, const void* k1, const 
     if (need > kStaticScratchBytes) return SA_ERR_WORKSPACE;      // the built-in scratch is fixed-size
     void* scratch = static_scratch();                             // first call per device resolves the address
     if (!scratch) return SA_ERR_LAUNCH;
-    // the scratch keeps what the previous call left: the status word must start at zero
-    if (cudaMemsetAsync(scratch, 0, kStatusBytes, static_cast<cudaStream_t>(stream)) != cudaSuccess) return SA_ERR_LAUNCH;
+    // The scratch keeps what the previous call left.  Nothing in it has to start at zero: the kernels
+    // write every partial sum before they read it, and the status word (zero when the library is
+    // loaded) is only ever cleared by sa_read_status_static, so that a timeout recorded by an earlier
+    // call is not lost.
     return sa_backward(p, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2, scratch, kStaticScratchBytes, stream);
 }
 

@@ -54,6 +54,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 struct WaitCtx {
     volatile int* abort_flag;    // shared memory
     DeviceStatus* status;        // global memory
+    uint64_t limit_ns;           // how long one wait may last before the block gives up
 };
 
 #ifdef SA_PROFILE
@@ -88,9 +89,9 @@ __device__ unsigned long long g_prof_count[64];
 #define SA_PROF_LIFE(t0) do { } while (0)
 #endif
 
-constexpr uint64_t kWaitLimitNs = 2000000000ull;   // 2 s: far beyond any legitimate wait in these kernels
+constexpr uint64_t kWaitLimitNs = 2000000000ull;   // default limit, 2 s: far beyond any legitimate wait in these kernels
 
-// Waits for the phase with the given parity.  Bounded: after kWaitLimitNs it records where it gave
+// Waits for the phase with the given parity.  Bounded: after ctx.limit_ns it records where it gave
 // up, raises the block's abort flag and returns false.
 __device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where);
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& ctx, int where) {
@@ -116,7 +117,7 @@ __device__ __forceinline__ bool mbar_wait_impl(uint64_t* bar, uint32_t parity, c
         if ((++spins & 0xff) == 0) {
             const uint64_t now = globaltimer_ns();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) {
+            else if (now - t0 > ctx.limit_ns) {
                 *ctx.abort_flag = 1;
                 if (atomicCAS(&ctx.status->code, 0, (int)SA_ERR_DEVICE_TIMEOUT) == 0) {
                     ctx.status->where = where;

@@ -64,6 +64,7 @@ struct BwdTcParams {
     float* ws_head_k2;       // [B,H,num_runs,w2-1,D]  partials for the rows just before a run
     float* ws_head_v2;
     DeviceStatus* status;
+    uint64_t wait_limit_ns;  // bound of every device-side wait
 };
 
 template <int HD, int NS = kRowStages>
@@ -280,7 +281,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     uint64_t* acc_free = sdp_ready + 5;               // dV1, dK1 read out (256 arrivals)
     uint32_t* tmem_slot = (uint32_t*)(smem + L::kMisc);
     volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
-    const WaitCtx wctx{abort_flag, P.status};
+    const WaitCtx wctx{abort_flag, P.status, P.wait_limit_ns};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     SA_PROF_T0(t_life);
@@ -676,7 +677,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     const BwdBars B = bwd_bars<NS>((uint64_t*)(smem + L::kBars));
     uint32_t* tmem_slot = (uint32_t*)(smem + L::kMisc);
     volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
-    const WaitCtx wctx{abort_flag, P.status};
+    const WaitCtx wctx{abort_flag, P.status, P.wait_limit_ns};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     SA_PROF_T0(t_life);
@@ -1121,7 +1122,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
     const BwdBars B = bwd_bars<NS>((uint64_t*)(smem + L::kBars));
     uint32_t* tmem_slot = (uint32_t*)(smem + L::kMisc);
     volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
-    const WaitCtx wctx{abort_flag, P.status};
+    const WaitCtx wctx{abort_flag, P.status, P.wait_limit_ns};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     SA_PROF_T0(t_life);
@@ -1516,7 +1517,9 @@ struct BwdPlan {
     size_t off_lse2, off_delta, off_full_k2, off_full_v2, off_head_k2, off_head_v2, total;
 };
 
-inline BwdPlan bwd_plan(const KParams& k) {
+// `sm_count`: multiprocessors of the device the launch will run on (the run length is chosen so that
+// there are at least two runs per multiprocessor).
+inline BwdPlan bwd_plan(const KParams& k, int sm_count) {
     BwdPlan pl{};
     int l = 0;
     while ((1 << l) < k.w2) ++l;
@@ -1524,7 +1527,7 @@ inline BwdPlan bwd_plan(const KParams& k) {
     pl.qpt = 128 >> l;
     const int units = (k.N + pl.qpt - 1) / pl.qpt;
     int upr = 16;
-    while (upr > 1 && (long)k.B * k.H * ((units + upr - 1) / upr) < 2 * 148) upr >>= 1;
+    while (upr > 1 && (long)k.B * k.H * ((units + upr - 1) / upr) < 2 * (long)sm_count) upr >>= 1;
     pl.units_per_run = upr;
     pl.num_runs = (units + upr - 1) / upr;
     auto align = [](size_t x) { return (x + 255) & ~(size_t)255; };
@@ -1541,7 +1544,7 @@ inline BwdPlan bwd_plan(const KParams& k) {
     return pl;
 }
 
-inline size_t bwd_workspace_bytes(const KParams& k) { return bwd_plan(k).total; }
+inline size_t bwd_workspace_bytes(const KParams& k, int sm_count) { return bwd_plan(k, sm_count).total; }
 
 typedef bool (*MakeMapFn)(CUtensorMap*, const void*, int, int, int, int, const sa_strides&, int);
 
@@ -1549,8 +1552,8 @@ typedef bool (*MakeMapFn)(CUtensorMap*, const void*, int, int, int, int, const s
 inline int launch_bwd(const KParams& k, const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
                       const void* o, const float* lse, const void* d_o, void* dq, void* dk1, void* dk2, void* dv1,
                       void* dv2, uint8_t* workspace, DeviceStatus* status, cudaStream_t st, int* nlaunch, MakeMapFn make_map,
-                      int sm_count) {
-    const BwdPlan pl = bwd_plan(k);
+                      int sm_count, uint64_t wait_limit_ns) {
+    const BwdPlan pl = bwd_plan(k, sm_count);
     BwdTcParams P{};
     P.k = k;
     P.dw_log2 = pl.dw_log2;
@@ -1568,6 +1571,7 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
     P.ws_head_k2 = (float*)(workspace + pl.off_head_k2);
     P.ws_head_v2 = (float*)(workspace + pl.off_head_v2);
     P.status = status;
+    P.wait_limit_ns = wait_limit_ns;
     auto bf = [](const void* x) { return (const __nv_bfloat16*)x; };
 
     const long rows = (long)k.B * k.H * k.N;

@@ -38,6 +38,7 @@ struct FwdTcParams {
     int num_qblocks;      // ceil(N / queries per unit)
     long num_units;       // B * H * num_qblocks
     DeviceStatus* status;
+    uint64_t wait_limit_ns;   // bound of every device-side wait
 };
 
 template <int HD>
@@ -111,7 +112,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
     uint64_t* p_ready = o_ready + kNumRowTiles;     // [kNumRowTiles][4]: P of one 32-column chunk stored
     uint32_t* tmem_base_slot = (uint32_t*)(smem + L::kMisc);
     volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
-    const WaitCtx wctx{abort_flag, P.status};
+    const WaitCtx wctx{abort_flag, P.status, P.wait_limit_ns};
 
     const int tid = threadIdx.x;
     SA_PROF_T0(t_life);

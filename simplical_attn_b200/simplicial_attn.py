@@ -83,6 +83,76 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class _StatusWatch:
+    """Surfaces device-side timeouts without a synchronisation per call.
+
+    After every launch the status word of the call's workspace is copied, stream-ordered, into a
+    pinned host slot and an event is recorded.  The next call on the same device looks at the slots
+    whose event has already completed (a non-blocking query) and raises if one of them holds an
+    error.  `flush()` synchronises and checks everything that is still pending."""
+
+    SLOTS = 32                      # pinned status slots per device, reused
+
+    def __init__(self):
+        self._dev = {}              # device index -> (pinned [SLOTS, 4] int32, free slot list, pending list)
+
+    def _state(self, index: int):
+        st = self._dev.get(index)
+        if st is None:
+            st = (torch.zeros(self.SLOTS, 4, dtype=torch.int32).pin_memory(), list(range(self.SLOTS)), [])
+            self._dev[index] = st
+        return st
+
+    def watch(self, ws: torch.Tensor, label: str) -> None:
+        host, free, pending = self._state(ws.device.index)
+        if not free:
+            self.poll(ws.device, wait_oldest=True)
+        i = free.pop()
+        host[i].copy_(ws[:16].view(torch.int32), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        pending.append((ev, i, label))
+
+    def poll(self, device: torch.device, wait: bool = False, wait_oldest: bool = False) -> None:
+        if device.index not in self._dev:
+            return
+        host, free, pending = self._state(device.index)
+        bad = None
+        keep = []
+        for n, (ev, i, label) in enumerate(pending):
+            if wait or (wait_oldest and n == 0):
+                ev.synchronize()
+            if ev.query():
+                code, where, block = (int(x) for x in host[i][:3])
+                if code != 0 and bad is None:
+                    bad = (label, code, where, block)
+                free.append(i)
+            else:
+                keep.append((ev, i, label))
+        pending[:] = keep
+        if bad is not None:
+            raise _abi.SimplicialAttnError(f"{bad[0]} (device side: wait site {bad[2]}, block {bad[3]})", bad[1])
+
+    def flush(self, device=None) -> None:
+        if device is None:
+            indices = list(self._dev)
+        else:
+            d = torch.device(device)
+            indices = [d.index if d.index is not None else torch.cuda.current_device()]
+        for index in indices:
+            self.poll(torch.device("cuda", index), wait=True)
+
+
+_status_watch = _StatusWatch()
+
+
+def check_device_status(device=None) -> None:
+    """Synchronises and raises `SimplicialAttnError` if a kernel of an earlier call on `device`
+    (default: every device used so far) gave up on a bounded wait.  Earlier calls are also checked,
+    without synchronising, at the start of every later call."""
+    _status_watch.flush(device)
+
+
 def two_simplicial_attn_fwd_kernel(q, k1, k2, v1, v2, w1, w2, scale, k2_bias=0.0, v2_bias=0.0, halo1=0, halo2=0,
                                    algo=None):
     """Forward launch (the reference's kernel of the same name, `simplicial/kernels.py:11-171`).
@@ -90,6 +160,7 @@ def two_simplicial_attn_fwd_kernel(q, k1, k2, v1, v2, w1, w2, scale, k2_bias=0.0
     lib = _abi.load()
     q, k1, k2, v1, v2 = (_unit_inner(t) for t in (q, k1, k2, v1, v2))
     B, N, H, Hkv, D = _check_inputs(q, k1, k2, v1, v2, halo1, halo2)
+    _status_watch.poll(q.device)
     o = torch.empty_like(q)                                   # triton_impl.py:23
     lse = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
     p = _make_params(q, k1, k2, v1, v2, o, w1, w2, scale, k2_bias, v2_bias, halo1, halo2, algo or default_algo)
@@ -99,6 +170,8 @@ def two_simplicial_attn_fwd_kernel(q, k1, k2, v1, v2, w1, w2, scale, k2_bias=0.0
     _abi.check("sa_forward", rc)
     if debug_device_status:
         _abi.check("sa_forward (device)", lib.sa_read_status(_ptr(ws), _stream()))
+    else:
+        _status_watch.watch(ws, "sa_forward")
     return o, lse
 
 
@@ -110,6 +183,7 @@ def two_simplicial_attn_bwd(q, k1, k2, v1, v2, o, lse, d_o, w1, w2, scale, k2_bi
     lib = _abi.load()
     q, k1, k2, v1, v2, o, d_o = (_unit_inner(t) for t in (q, k1, k2, v1, v2, o, d_o))
     _check_inputs(q, k1, k2, v1, v2, halo1, halo2)
+    _status_watch.poll(q.device)
     grads = [torch.empty_like(t) if n else None for t, n in zip((q, k1, k2, v1, v2), need)]
     p = _make_params(q, k1, k2, v1, v2, o, w1, w2, scale, k2_bias, v2_bias, halo1, halo2, algo or default_algo)
     p.d_o = _strides(d_o)
@@ -120,10 +194,13 @@ def two_simplicial_attn_bwd(q, k1, k2, v1, v2, o, lse, d_o, w1, w2, scale, k2_bi
     _abi.check("sa_backward", rc)
     if debug_device_status:
         _abi.check("sa_backward (device)", lib.sa_read_status(_ptr(ws), _stream()))
+    else:
+        _status_watch.watch(ws, "sa_backward")
     return tuple(grads)
 
 
-# When true every call synchronises and raises if a device-side bounded wait gave up.
+# When true every call synchronises and raises at once if a device-side bounded wait gave up; otherwise
+# such a timeout is raised by the next call after the kernels have finished, or by check_device_status().
 debug_device_status = False
 
 

@@ -282,6 +282,44 @@ def test_grouped_heads_full_size():
         assert so.rel_l2(a.float().cpu(), b.float().cpu()) <= TOL_G_BF16, nm
 
 
+# B, N, H, Hkv, D, w1, w2 -- the sizes the headline figures are quoted on
+FULL_SIZE_GRAD_CASES = [
+    pytest.param((2, 8192, 8, 8, 128, 512, 32), id="B2_H8_N8192_w512x32"),          # single-GPU forward / headline windows
+    pytest.param((1, 16384, 32, 2, 128, 512, 32), id="B1_H32_Hkv2_N16384_w512x32"), # grouped heads: 16 query heads per KV head
+    pytest.param((1, 8192, 2, 2, 128, 1024, 64), id="B1_H2_N8192_w1024x64"),        # the long-sequence configuration's windows
+]
+
+
+@pytest.mark.parametrize("case", FULL_SIZE_GRAD_CASES)
+def test_full_size_gradients_vs_oracle(case):
+    """All five gradients of the tensor-core path at full sequence length against the C loop oracle
+    (`simplicial/reference.py:39-74` through the pinned C port), on ranges the oracle finishes in
+    seconds.  For a range of 64 K rows [k0, k0+64) the oracle is run on every query row that reaches
+    it, [k0, k0+64+w1-1): that gives dK1, dV1, dK2 and dV2 of the K rows complete (the sum of the
+    shares of those queries) and dQ of all those query rows.  Ranges: the sequence start, an
+    unaligned range in the interior; plus dQ of the last rows."""
+    B, N, H, Hkv, D, w1, w2 = case
+    scale = 1.0 / math.sqrt(D)
+    q, k1, k2, v1, v2, do = so.make_inputs(B, N, H, Hkv, D, seed=17, seed_do=18)
+    cfg = dict(w1=w1, w2=w2, scale=scale, k2_bias=0.0, v2_bias=0.0)
+    ins = dict(q=q, k1=k1, k2=k2, v1=v1, v2=v2, do=do)
+    _, _, grads = _run(ins, cfg, "tcgen05")
+    dq, dk1, dk2, dv1, dv2 = (g.float().cpu() for g in grads)
+    assert all(bool(torch.isfinite(g).all()) for g in (dq, dk1, dk2, dv1, dv2))
+    for k0 in (0, N // 2 + 37):
+        r0, r1 = k0, min(N, k0 + 64 + w1 - 1)
+        ref = c_oracle.backward(q, k1, k2, v1, v2, do, w1, w2, scale, row_begin=r0, row_end=r1)
+        assert so.rel_l2(dq[:, r0:r1], ref[0][:, r0:r1]) <= TOL_G_BF16, ("dq", k0)
+        for nm, g, r in zip(("dk1", "dk2", "dv1", "dv2"), (dk1, dk2, dv1, dv2), ref[1:]):
+            assert so.rel_l2(g[:, k0:k0 + 64], r[:, k0:k0 + 64]) <= TOL_G_BF16, (nm, k0)
+    r0 = N - 24
+    ref = c_oracle.backward(q, k1, k2, v1, v2, do, w1, w2, scale, row_begin=r0, row_end=N)
+    assert so.rel_l2(dq[:, r0:], ref[0][:, r0:]) <= TOL_G_BF16, "dq (end)"
+    # the last K rows receive gradient only from the last queries: complete in this call as well
+    for nm, g, r in zip(("dk1", "dk2", "dv1", "dv2"), (dk1, dk2, dv1, dv2), ref[1:]):
+        assert so.rel_l2(g[:, N - 1:], r[:, N - 1:]) <= TOL_G_BF16, (nm, "last row")
+
+
 def test_host_pipeline_matches_device_call():
     """Pinned host tensors in, pinned host results out (chunked uploads / kernels / downloads on three
     streams).  O, dQ, dK1, dV1 are bit-identical to one device call on the whole batch; dK2 and dV2 are

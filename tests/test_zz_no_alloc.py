@@ -1,9 +1,11 @@
 """The allocation-free backward entry point, sa_backward_static.
 
-Some callers of this library must not allocate device memory while they call it: code running
-under a CUDA stream capture, inside an allocator callback of the host framework, or in a process
-whose device memory has been handed out completely.  For them the library carries a fixed scratch
-array in its own image and sa_backward_static uses it in place of a caller workspace.
+Some callers of this library cannot get a device workspace at the moment they need gradients: a
+plugin that runs inside the host framework's allocator callback (asking the allocator again would
+re-enter it), a worker in a process whose device memory has been handed out completely to a pool it
+does not own (a cudaMalloc simply fails), a loop that must not take the allocation lock.  For them
+the library carries a fixed 32 MiB scratch array in its own image, and sa_backward_static uses it in
+place of a caller workspace.
 
 This file is collected last on purpose: it checks the entry point against the regular sa_backward
 (same inputs, same outputs expected) on two consecutive calls -- the second call finds the scratch
@@ -33,10 +35,11 @@ def _problem(seed, B, N, H, Hkv, D, w1, w2):
     return dev, o, lse, scale, ref
 
 
-def _call_static(dev, o, lse, scale, w1, w2):
+def _call_static(dev, o, lse, scale, w1, w2, grads=None):
     lib = _abi.load()
     q, k1, k2, v1, v2, do = dev
-    grads = [torch.empty_like(t) for t in (q, k1, k2, v1, v2)]
+    if grads is None:
+        grads = [torch.empty_like(t) for t in (q, k1, k2, v1, v2)]
     p = host._make_params(q, k1, k2, v1, v2, o, w1, w2, scale, 0.0, 0.0, 0, 0, "auto")
     p.d_o = host._strides(do)
     p.dq, p.dk1, p.dk2, p.dv1, p.dv2 = (host._strides(g) for g in grads)
@@ -47,13 +50,24 @@ def _call_static(dev, o, lse, scale, w1, w2):
     return rc, grads
 
 
+def _free_bytes():
+    torch.cuda.synchronize()
+    return torch.cuda.mem_get_info()[0]
+
+
 def test_static_backward_matches_workspace_backward_twice():
     # two different problems back to back: the second call reuses the scratch the first one filled
     for seed, shape in ((21, (1, 384, 4, 2, 128, 160, 32)), (33, (2, 200, 2, 2, 64, 48, 16))):
         B, N, H, Hkv, D, w1, w2 = shape
         dev, o, lse, scale, ref = _problem(seed, B, N, H, Hkv, D, w1, w2)
-        rc, grads = _call_static(dev, o, lse, scale, w1, w2)
+        _call_static(dev, o, lse, scale, w1, w2)          # first use on this device resolves the scratch address
+        grads = [torch.empty_like(t) for t in dev[:5]]
+        free_before = _free_bytes()
+        rc, grads = _call_static(dev, o, lse, scale, w1, w2, grads)
         assert rc == _abi.SA_OK, _abi.strerror(rc)
+        assert _free_bytes() == free_before, "the call changed the amount of free device memory"
+        # the scratch's own status word: nothing timed out, and it is read through its own reader
+        assert _abi.load().sa_read_status_static(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)) == _abi.SA_OK
         for name, g, r in zip(("dq", "dk1", "dk2", "dv1", "dv2"), grads, ref):
             assert so.rel_l2(g.float().cpu(), r.float().cpu()) <= 1e-2, name      # the gradient tolerance of the parity tests
             assert torch.equal(g, r), name                                          # same kernels, same order: same bits
