@@ -17,7 +17,12 @@ the kernels by batch chunks.  `roofline` describes the dominant kernel; `cpu_bas
 times the C loop oracle on the host cores on a bounded sample of the same workload.
 
 `--impl reference` times the reference's algorithm on the host cores (the C restatement of its
-loop; the reference itself is a Python triple loop that does not reach these sizes).
+loop; the reference itself is a Python triple loop that does not reach these sizes), with every
+core the process may use.
+
+With two or more ranks the line also carries `c4_sharded`: the long-sequence configuration (B1 H16
+N65536 D128 w1=1024 w2=64) split along N over the ranks, halo exchange inside the timed region, with
+the rows at a rank boundary checked against the CPU oracle.
 """
 from __future__ import annotations
 
@@ -37,11 +42,30 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOAD = dict(B=16, H=16, Hkv=16, N=8192, D=128, w1=512, w2=32)
+LONG_SEQUENCE = dict(B=1, H=16, Hkv=16, N=65536, D=128, w1=1024, w2=64)     # split along N over the ranks
+# DRAM bytes per launch of each big kernel for ONE batch element of WORKLOAD (dram__bytes_read.sum +
+# dram__bytes_write.sum of the ncu captures summarised under profiles/), and the library version those
+# captures were taken with: the figures are only reported while the library still has that version.
+TRAFFIC = dict(lib_version=100, fwd_tc_kernel=194.6e6, bwd_col_kernel=247.0e6, bwd_row_kernel=395.0e6)
 FALLBACK_PEAKS = dict(bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, hbm_gbs=6650.0)
 
 
 def flops_unit(B, H, N, D, w1, w2):
+    """One trilinear contraction over nominal (full) windows: 2*B*H*N*w1*w2*D."""
     return 2.0 * B * H * N * w1 * w2 * D
+
+
+def flops_unit_exact(B, H, N, D, w1, w2):
+    """The same over the (j, k) pairs that exist: the first rows of a sequence have shorter windows."""
+    triples = sum(min(i + 1, w1) * min(i + 1, w2) for i in range(min(N, max(w1, w2)))) + max(0, N - max(w1, w2)) * w1 * w2
+    return 2.0 * B * H * D * triples
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
 def load_peaks():
@@ -125,7 +149,8 @@ def cpu_oracle_rate(cfg, target_s=12.0, threads=None):
     from oracle import c_oracle, simplicial_oracle as so
     D, w1, w2 = cfg["D"], cfg["w1"], cfg["w2"]
     scale = 1.0 / math.sqrt(D)
-    cores = c_oracle.num_threads()
+    # every core this process may run on, whatever OMP_NUM_THREADS a launcher exported
+    cores = c_oracle.set_threads(threads or host_threads())
 
     def run(R):
         q, k1, k2, v1, v2, do = so.make_inputs(1, R, 1, 1, D, seed=5, seed_do=6, halo1=w1 - 1, halo2=w2 - 1)
@@ -143,6 +168,22 @@ def cpu_oracle_rate(cfg, target_s=12.0, threads=None):
     return fl / t / 1e12, cores, R, t
 
 
+def cpu_oracle_c1():
+    """Seconds the C loop oracle takes for the reference's own CPU-runnable case in full (B1 H2 N256
+    D64 w1=64 w2=16): forward, and forward + backward."""
+    from oracle import c_oracle, simplicial_oracle as so
+    q, k1, k2, v1, v2, do = so.make_inputs(1, 256, 2, 2, 64, seed=0, seed_do=1, bf16_round=False)
+    scale = 1.0 / math.sqrt(64)
+    t0 = time.perf_counter()
+    c_oracle.forward(q, k1, k2, v1, v2, 64, 16, scale)
+    t1 = time.perf_counter()
+    c_oracle.backward(q, k1, k2, v1, v2, do, 64, 16, scale)
+    t2 = time.perf_counter()
+    return {"config": "B1 H2 N256 D64 w1=64 w2=16 fp32", "forward_s": t1 - t0, "forward_backward_s": t2 - t0,
+            "note": "C restatement of the loop; the reference's own Python loop is unavailable on this box "
+                    "(the reference checkout does not travel)"}
+
+
 def run_reference_arm(args, cfg):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -156,13 +197,16 @@ def run_reference_arm(args, cfg):
             per_step.append((rate, t))
     value = statistics.mean(r for r, _ in per_step)
     ms = statistics.mean(t for _, t in per_step) * 1e3
-    sample = f"forward+backward of {rows} query rows of one (batch, head), full windows, per step"
+    sample = (f"forward+backward of {rows} query rows of one (batch, head), full windows, per step; the rate is "
+              f"extrapolated to the workload, ms_per_step is the sample's time")
     line = {
         "impl": "reference", "metric": "fwd+bwd TFLOP/s (N=8192,D=128,w1=512,w2=32)", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": workload_name(cfg), **cfg, "parallelism": "host cores"},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "config": {"workload": workload_name(cfg), **cfg},
+        "parallelism": f"{cores} host threads (OpenMP)",
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample,
+                         "extrapolated": True, "c1_full": cpu_oracle_c1()},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -172,6 +216,114 @@ def run_reference_arm(args, cfg):
 def workload_name(cfg):
     return (f"batch x head-parallel fwd+bwd B{cfg['B']} H{cfg['H']} Hkv{cfg['Hkv']} N{cfg['N']} D{cfg['D']} "
             f"w1={cfg['w1']} w2={cfg['w2']}")
+
+
+def run_shape_sweeps(sab, device, timed):
+    """The reference's own sweeps (simplicial/test_performance.py:409-482: sequence length, batch,
+    heads, head dim and window at its small base shape B2 H4 N512 D64 w 32/32), forward and
+    forward + backward, bf16.  Head dims outside the tensor-core kernels run on the general kernels."""
+    base = dict(B=2, N=512, H=4, D=64, w=32)
+    grids = {"N": [64, 128, 256, 512, 1024, 2048], "B": [1, 2, 4, 8, 16, 32], "H": [1, 2, 4, 8, 16, 32],
+             "D": [32, 64, 128, 256, 512], "w": [8, 16, 32, 64, 128, 256]}
+    out = []
+    for axis, values in grids.items():
+        for v in values:
+            c = dict(base)
+            c[axis] = v
+            pt = {"axis": axis, **c}
+            if c["D"] > 256:
+                pt["unsupported"] = "head dim above 256"
+                out.append(pt)
+                continue
+            g = torch.Generator(device="cpu").manual_seed(1)
+            ts = [torch.randn(c["B"], c["N"], c["H"], c["D"], generator=g).to(torch.bfloat16).to(device) for _ in range(6)]
+            scale = 1.0 / math.sqrt(c["D"])
+            fwd = lambda: sab.two_simplicial_attn_fwd_kernel(*ts[:5], c["w"], c["w"], scale)
+            o_, lse_ = fwd()
+            both = lambda: sab.two_simplicial_attn_bwd(*ts[:5], *sab.two_simplicial_attn_fwd_kernel(*ts[:5], c["w"], c["w"], scale),
+                                                       ts[5], c["w"], c["w"], scale)
+            pt["fwd_ms"] = timed(fwd, 5, 2)
+            pt["fwd_bwd_ms"] = timed(both, 5, 2)
+            u = flops_unit(c["B"], c["H"], c["N"], c["D"], min(c["w"], c["N"]), min(c["w"], c["N"]))
+            pt["fwd_bwd_tflops"] = 8.0 * u / (pt["fwd_bwd_ms"] * 1e-3) / 1e12
+            out.append(pt)
+    return out
+
+
+def run_long_sequence_sharded(dist, device, rank, world, args, barrier):
+    """The long-sequence configuration split along N: every rank owns N/world query rows and receives
+    the (w1-1)-row K1/V1 and (w2-1)-row K2/V2 halos from its predecessor (one batched NCCL exchange per
+    direction, inside the timed region).  Rows at the boundary between ranks 0 and 1 are checked
+    against the C loop oracle."""
+    from simplical_attn_b200 import sharded
+    cfg = dict(LONG_SEQUENCE)
+    B, H, Hkv, N, D, w1, w2 = (cfg[k] for k in ("B", "H", "Hkv", "N", "D", "w1", "w2"))
+    scale = 1.0 / math.sqrt(D)
+    s0, s1 = sharded.shard_bounds(N, world, rank)
+    n = s1 - s0
+    g = torch.Generator(device="cpu").manual_seed(4000 + rank)
+    loc = [torch.randn(B, n, H if i == 0 else Hkv, D, generator=g).to(torch.bfloat16).to(device) for i in range(5)]
+    do = torch.randn(B, n, H, D, generator=g).to(torch.bfloat16).to(device)
+    leaves = [t.requires_grad_(True) for t in loc]
+
+    def step():
+        for t in leaves:
+            t.grad = None
+        o = sharded.two_simplicial_attention_sharded(*leaves, w1, w2, N, scale)
+        o.backward(do)
+        return o
+
+    def timed_max(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(steps):
+            fn()
+        ev1.record()
+        barrier()
+        t = torch.tensor([ev0.elapsed_time(ev1) / steps], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    steps = max(2, min(args.steps, 5))
+    ms = timed_max(step, steps, 2)
+    h1, h2 = sharded.halo_rows(w1, s0), sharded.halo_rows(w2, s0)
+    e1 = sharded.halo_rows(w1, s1) if rank < world - 1 else 0
+    e2 = sharded.halo_rows(w2, s1) if rank < world - 1 else 0
+    with torch.no_grad():
+        halo_ms = timed_max(lambda: sharded._HaloExchange.apply(*[t.detach() for t in leaves[1:]], h1, h2, e1, e2, None), 5, 2)
+
+    # boundary rows: the first rows of rank 1 see the halo over their whole windows
+    check_rows = 8
+    with torch.no_grad():
+        o = sharded.two_simplicial_attention_sharded(*[t.detach() for t in leaves], w1, w2, N, scale)
+    err = None
+    tail = w1 - 1 + 64
+    if rank == 1:
+        pack = [o[:, :check_rows].contiguous()] + [t.detach()[:, :check_rows].contiguous() for t in leaves]
+        for req in dist.batch_isend_irecv([dist.P2POp(dist.isend, t, 0) for t in pack]):
+            req.wait()
+    if rank == 0:
+        got = [torch.empty(B, check_rows, H if i in (0, 1) else Hkv, D, dtype=torch.bfloat16, device=device) for i in range(6)]
+        for req in dist.batch_isend_irecv([dist.P2POp(dist.irecv, t, 1) for t in got]):
+            req.wait()
+        torch.cuda.synchronize()
+        from oracle import c_oracle
+        c_oracle.set_threads(host_threads())
+        parts = [torch.cat([a.detach()[:, n - tail:], b], dim=1).float().cpu() for a, b in zip(leaves, got[1:])]
+        ro, _ = c_oracle.forward(*parts, w1, w2, scale, row_begin=tail, row_end=tail + check_rows)
+        err = float((got[0].float().cpu() - ro[:, tail:tail + check_rows]).abs().max())
+    barrier()
+    u = flops_unit(B, H, N, D, w1, w2)
+    tf = 8.0 * u / (ms * 1e-3) / 1e12
+    return {"workload": f"fwd+bwd B{B} H{H} N{N} D{D} w1={w1} w2={w2} split along N over {world} ranks ({n} rows each)",
+            "tflops": tf, "tflops_per_gpu": tf / world, "ms_per_step": ms, "halo_ms": halo_ms, "steps": steps,
+            "halo_bytes_per_rank_each_way": 2 * ((w1 - 1) + (w2 - 1)) * Hkv * D * 2,
+            "frac_of_nominal_2250": tf / world / 2250.0,
+            "boundary_rows_checked": f"rows {s1 if rank == 0 else ''}..+{check_rows} (first rows of rank 1) against the C loop oracle",
+            "boundary_max_abs_err": err}
 
 
 def main():
@@ -185,6 +337,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--sweep", action="store_true",
                     help="also time the window sweep w1 in {128,256,512,1024} x w2 in {16,32,64} (adds a 'sweep' key)")
+    ap.add_argument("--shape-sweeps", action="store_true",
+                    help="also time the reference's own sweeps over N, B, H, D and w (adds a 'shape_sweeps' key)")
+    ap.add_argument("--no-sharded", action="store_true", help="skip the sequence-sharded configuration at 2+ ranks")
     args = ap.parse_args()
     cfg = dict(WORKLOAD)
     if args.batch is not None:
@@ -304,9 +459,16 @@ def main():
 
     ms_e2e = None
     if not args.no_e2e:
-        ms_e2e = timed(step_e2e, max(1, min(args.steps, 3)), 1)
+        ms_e2e = timed(step_e2e, args.steps, args.warmup)
+
+    shape_sweeps = run_shape_sweeps(sab, device, timed) if args.shape_sweeps else None
+
+    c4 = None
+    if world > 1 and not args.no_sharded:
+        c4 = run_long_sequence_sharded(dist, device, rank, world, args, barrier)
 
     unit_total = flops_unit(cfg["B"], cfg["H"], cfg["N"], D, w1, w2)
+    unit_exact = flops_unit_exact(cfg["B"], cfg["H"], cfg["N"], D, w1, w2)
     unit_rank = unit_total / world
     value = 8.0 * unit_total / (ms_step * 1e-3) / 1e12
 
@@ -325,17 +487,21 @@ def main():
         # (S, P.V1); column kernel 3 (dV1, dK1 and half of the shared S/dP recomputation); row kernel 3
         # (G, U and the other half).  DRAM traffic per launch comes from the ncu capture of a one-batch
         # case (profiles/), scaled by the rank's batch: traffic grows in proportion to the batch.
+        lib_version = int(_abi.load().sa_version())
+        traffic_ok = algo == 2 and lib_version == TRAFFIC["lib_version"]
         kernels = {
-            "fwd_tc_kernel": (ms_fwd, 2.0 * unit_rank, 194.6e6 * Bl),
-            "bwd_col_kernel": (ms_col, 3.0 * unit_rank, 247.0e6 * Bl),
-            "bwd_row_kernel": (ms_row, 3.0 * unit_rank, 395.0e6 * Bl),
+            "fwd_tc_kernel": (ms_fwd, 2.0 * unit_rank, TRAFFIC["fwd_tc_kernel"] * Bl),
+            "bwd_col_kernel": (ms_col, 3.0 * unit_rank, TRAFFIC["bwd_col_kernel"] * Bl),
+            "bwd_row_kernel": (ms_row, 3.0 * unit_rank, TRAFFIC["bwd_row_kernel"] * Bl),
         }
         dom = max(kernels, key=lambda k: kernels[k][0])
         dom_ms, dom_fl, dom_traffic = kernels[dom]
         achieved = dom_fl / (dom_ms * 1e-3) / 1e12
         roof = {"bound": "tensor", "kernel": f"{dom} ({family})", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                 "frac": achieved / peak, "peak_source": f"{peak_kind} bf16 sustained (cuBLAS)",
-                "traffic": dom_traffic if algo == 2 else None, "traffic_unit": "bytes per launch (ncu, scaled from batch 1)",
+                "traffic": dom_traffic if traffic_ok else None,
+                "traffic_unit": f"bytes per launch (ncu capture of one batch element with library version "
+                                f"{TRAFFIC['lib_version']}, scaled by the rank's batch; null when the library differs)",
                 "frac_of_nominal_2250": achieved / 2250.0,
                 "per_kernel": {k: {"ms": v[0], "tflops": v[1] / (v[0] * 1e-3) / 1e12, "frac": v[1] / (v[0] * 1e-3) / 1e12 / peak}
                                for k, v in kernels.items()},
@@ -345,12 +511,22 @@ def main():
             "metric": "fwd+bwd TFLOP/s (N=8192,D=128,w1=512,w2=32)", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": workload_name(cfg), **cfg, "parallelism": f"batch split over {world} GPU(s)",
-                       "l2": "inputs (6 x %.0f MB per rank) exceed the 126 MB L2" % (q.numel() * 2 / 1e6),
-                       "kernels": family},
+            "config": {"workload": workload_name(cfg), **cfg},
+            "parallelism": f"batch split over {world} GPU(s)",
+            "l2": "inputs (6 x %.0f MB per rank) exceed the 126 MB L2" % (q.numel() * 2 / 1e6),
+            "kernels": family, "library_version": lib_version,
+            "flops": {"per_step_nominal_8U": 8.0 * unit_total, "per_step_exact_triples": 8.0 * unit_exact,
+                      "exact_over_nominal": unit_exact / unit_total,
+                      "value_exact_triples": 8.0 * unit_exact / (ms_step * 1e-3) / 1e12,
+                      "note": "value counts nominal full windows (2*B*H*N*w1*w2*D per contraction, 8 per step); the exact "
+                              "figure counts the (j,k) pairs that exist (the first rows of a sequence have shorter windows)"},
             "frac_of_peak": {"measured_sustained": value / world / peak, "nominal_2250": value / world / 2250.0},
             "clocks": clocks, "gpu_launches": launches, "roofline": roof,
         }
+        if shape_sweeps is not None:
+            line["shape_sweeps"] = shape_sweeps
+        if c4 is not None:
+            line["c4_sharded"] = c4
         if sweep is not None:
             for pt in sweep:
                 pt["frac_of_measured_peak"] = pt["tflops"] / world / peak
@@ -365,7 +541,8 @@ def main():
             rate, cores, rows, t = cpu_oracle_rate(cfg)
             line["cpu_baseline"] = {"value": rate, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                     "sample": f"C loop oracle, forward+backward of {rows} query rows of one "
-                                              f"(batch, head) with full windows, {t:.1f} s"}
+                                              f"(batch, head) with full windows, {t:.1f} s",
+                                    "extrapolated": True, "c1_full": cpu_oracle_c1()}
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()

@@ -138,6 +138,14 @@ int sa_selftest_wait_timeout(void* workspace, uint64_t limit_ns, void* stream);
  * sa_status if `p` is invalid. */
 int sa_resolve_algo(const sa_params* p);
 
+/* Strided copy between host and device (either direction, or device to device) on `stream`: `rows`
+ * pieces of `row_bytes` bytes, `src_pitch` / `dst_pitch` bytes apart.  Used to move one group of
+ * heads of a [B, N, H, D] tensor that lives in pinned host memory without staging it first.  Host
+ * memory must be pinned for the copy to overlap with kernels.  No counterpart in the reference
+ * (its tensors never leave the device). */
+int sa_copy_rows_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes,
+                       size_t rows, void* stream);
+
 /* Number of kernels this library has launched in this process so far (all devices, all streams).
  * No counterpart in the reference. */
 uint64_t sa_kernel_launches(void);

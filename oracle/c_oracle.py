@@ -45,6 +45,12 @@ def num_threads() -> int:
     return int(lib().sa_oracle_num_threads())
 
 
+def set_threads(n: int) -> int:
+    """Use `n` OpenMP threads from now on (launchers such as torchrun export OMP_NUM_THREADS=1)."""
+    lib().sa_oracle_set_threads(ctypes.c_int(int(n)))
+    return num_threads()
+
+
 def _f32(t):
     t = t.detach().to(torch.float32).contiguous()
     return t, ctypes.c_void_p(t.data_ptr())

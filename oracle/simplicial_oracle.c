@@ -46,6 +46,15 @@ int sa_oracle_num_threads(void) {
 #endif
 }
 
+/* Sets the number of OpenMP threads the loops use (a launcher may have exported OMP_NUM_THREADS=1). */
+void sa_oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 /* One query row: fills o_row[D] and returns the natural-log softmax denominator.
  * `p_out` (may be NULL) receives the normalised weights, laid out [j - j_lo][k - k_lo]. */
 static double row_forward(const sa_oracle_dims *p, const float *qrow, const float *k1h, const float *k2h,

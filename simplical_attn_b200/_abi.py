@@ -18,7 +18,7 @@ SA_ALGO_AUTO, SA_ALGO_GENERAL, SA_ALGO_TCGEN05 = 0, 1, 2
 EXPORTS = ("sa_forward", "sa_backward", "sa_forward_workspace_size", "sa_backward_workspace_size", "sa_read_status",
            "sa_resolve_algo", "sa_strerror", "sa_version", "sa_kernel_launches", "sa_backward_static",
            "sa_backward_static_capacity", "sa_read_status_static", "sa_read_status_ex", "sa_set_wait_limit_ns",
-           "sa_selftest_wait_timeout")
+           "sa_selftest_wait_timeout", "sa_copy_rows_async")
 
 
 class Strides(ctypes.Structure):
@@ -78,6 +78,8 @@ def load():
     lib.sa_set_wait_limit_ns.restype = None
     lib.sa_selftest_wait_timeout.argtypes = [vp, ctypes.c_uint64, vp]
     lib.sa_selftest_wait_timeout.restype = ctypes.c_int
+    lib.sa_copy_rows_async.argtypes = [vp, sz, vp, sz, sz, sz, vp]
+    lib.sa_copy_rows_async.restype = ctypes.c_int
     lib.sa_resolve_algo.argtypes = [pp]
     lib.sa_resolve_algo.restype = ctypes.c_int
     lib.sa_strerror.argtypes = [ctypes.c_int]

@@ -223,7 +223,7 @@ int resolve(const sa_params* p, bool backward) {
 
 extern "C" {
 
-int sa_version(void) { return 100; }
+int sa_version(void) { return 200; }
 
 uint64_t sa_kernel_launches(void) { return g_launches.load(); }
 
@@ -359,6 +359,15 @@ int sa_backward(const sa_params* p, const void* q, const void* k1, const void* k
     }
     const cudaError_t e = sa::general::launch_bwd(p->dtype, k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2, st);
     g_launches += (dq ? 1 : 0) + ((dk1 || dv1) ? 1 : 0) + ((dk2 || dv2) ? 1 : 0);
+    return e == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
+}
+
+int sa_copy_rows_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t row_bytes, size_t rows,
+                       void* stream) {
+    if (!dst || !src) return SA_ERR_NULL_POINTER;
+    if (row_bytes > dst_pitch || row_bytes > src_pitch) return SA_ERR_BAD_STRIDE;
+    const cudaError_t e = cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, row_bytes, rows, cudaMemcpyDefault,
+                                            static_cast<cudaStream_t>(stream));
     return e == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
 }
 

@@ -83,3 +83,16 @@ def test_python_layer_rejects_cpu_tensors():
         sab.two_simplicial_attention(x, x, x, x, x, 4, 4)
     m = sab.TwoSimplicialAttention(16, 4, 4)
     assert len(m.state_dict()) == 0 and abs(m.scale - 0.25) < 1e-12
+
+
+def test_host_pipeline_chunk_plan():
+    from simplical_attn_b200.host_pipeline import plan_chunks
+    # whole sequences in the middle, a small head group first and last
+    assert plan_chunks(3, 16) == [(0, 0, 4), (0, 4, 16), (1, 0, 16), (2, 0, 12), (2, 12, 16)]
+    assert plan_chunks(1, 16) == [(0, 0, 4), (0, 4, 12), (0, 12, 16)]
+    assert plan_chunks(2, 1) == [(0, 0, 1), (1, 0, 1)]
+    assert plan_chunks(1, 2) == [(0, 0, 1), (0, 1, 2)]
+    for B, Hkv in ((1, 1), (2, 2), (5, 3), (16, 16), (2, 8)):
+        ch = plan_chunks(B, Hkv)
+        assert sorted(ch) == ch and all(h1 > h0 for _, h0, h1 in ch)
+        assert sum(h1 - h0 for _, h0, h1 in ch) == B * Hkv

@@ -320,16 +320,20 @@ def test_full_size_gradients_vs_oracle(case):
         assert so.rel_l2(g[:, N - 1:], r[:, N - 1:]) <= TOL_G_BF16, (nm, "last row")
 
 
-def test_host_pipeline_matches_device_call():
-    """Pinned host tensors in, pinned host results out (chunked uploads / kernels / downloads on three
-    streams).  O, dQ, dK1, dV1 are bit-identical to one device call on the whole batch; dK2 and dV2 are
-    sums of per-run partials whose run length depends on the batch size, so they agree to fp32
-    rounding of the partial sums (well inside bf16 resolution)."""
-    from simplical_attn_b200.host_pipeline import HostPipeline
-    B, N, H, Hkv, D, w1, w2 = 5, 512, 4, 2, 128, 128, 32
+@pytest.mark.parametrize("shape", [(5, 512, 4, 2, 128, 128, 32), (1, 384, 8, 8, 128, 96, 16), (2, 256, 8, 2, 64, 64, 32)])
+def test_host_pipeline_matches_device_call(shape):
+    """Pinned host tensors in, pinned host results out (uploads / kernels / downloads of (sequence,
+    head-group) chunks on three streams, strided copies for the head groups).  O, dQ, dK1, dV1 are
+    bit-identical to one device call on the whole batch; dK2 and dV2 are sums of per-run partials whose
+    run length depends on how many (batch, head) pairs a call holds, so they agree to fp32 rounding of
+    the partial sums (well inside bf16 resolution)."""
+    from simplical_attn_b200.host_pipeline import HostPipeline, plan_chunks
+    B, N, H, Hkv, D, w1, w2 = shape
     ts = [t.to(torch.bfloat16).pin_memory() for t in so.make_inputs(B, N, H, Hkv, D, seed=9, seed_do=10)]
     scale = 1.0 / math.sqrt(D)
-    pipe = HostPipeline("cuda", chunk=2)
+    chunks = plan_chunks(B, Hkv)
+    assert sorted(chunks) == chunks and sum(h1 - h0 for _, h0, h1 in chunks) == B * Hkv      # every (sequence, KV head) once
+    pipe = HostPipeline("cuda")
     for _ in range(2):                                   # second call reuses buffers
         res = pipe.forward_backward(*ts, w1, w2, scale)
     dev = [t.cuda() for t in ts]

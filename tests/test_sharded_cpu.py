@@ -26,7 +26,7 @@ def _oracle_attn(q, k1, k2, v1, v2, w1, w2, scale, k2_bias, v2_bias, halo1, halo
     return so.forward(q, k1, k2, v1, v2, w1, w2, scale, k2_bias, v2_bias, halo1, halo2)[0]
 
 
-def _worker(rank, world, port, cfg, out_dir):
+def _worker(rank, world, port, cfg, out_dir, use_buffers=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -35,21 +35,32 @@ def _worker(rank, world, port, cfg, out_dir):
         q, k1, k2, v1, v2, do = so.make_inputs(B, N, H, Hkv, D, seed=7, seed_do=8)
         s, e = sharded.shard_bounds(N, world, rank)
         loc = [t[:, s:e].clone().requires_grad_(True) for t in (q, k1, k2, v1, v2)]
-        o = sharded.two_simplicial_attention_sharded(*loc, w1, w2, N, scale=0.2, attn_fn=_oracle_attn)
+        args = list(loc)
+        if use_buffers:
+            # the caller writes its K/V rows straight into the tail of a [halo | shard] buffer: no copy inside
+            for i, w in ((1, w1), (2, w2), (3, w1), (4, w2)):
+                h = sharded.halo_rows(w, s)
+                buf = sharded.kv_buffer(B, e - s, Hkv, D, h, loc[i].dtype, loc[i].device)
+                view = sharded.local_rows(buf, h)
+                view.copy_(loc[i])
+                args[i] = view
+        o = sharded.two_simplicial_attention_sharded(*args, w1, w2, N, scale=0.2, attn_fn=_oracle_attn)
         o.backward(do[:, s:e])
         torch.save({"o": o.detach(), "grads": [t.grad for t in loc], "range": (s, e)}, os.path.join(out_dir, f"r{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,cfg", [
-    (2, (1, 48, 2, 1, 16, 12, 5)),
-    (3, (2, 50, 2, 2, 16, 9, 9)),          # uneven shards 17/17/16
-    (2, (1, 40, 2, 2, 16, 21, 3)),         # halo as long as a shard allows
+@pytest.mark.parametrize("world,cfg,use_buffers", [
+    (2, (1, 48, 2, 1, 16, 12, 5), False),
+    (3, (2, 50, 2, 2, 16, 9, 9), False),          # uneven shards 17/17/16, batch 2 (halo through a staging buffer)
+    (2, (1, 40, 2, 2, 16, 21, 3), False),         # halo as long as a shard allows
+    (3, (1, 45, 2, 1, 16, 11, 4), True),          # K/V written by the caller into [halo | shard] buffers
+    (2, (2, 36, 2, 2, 16, 8, 8), True),
 ])
-def test_sharded_equals_unsharded(world, cfg, tmp_path):
+def test_sharded_equals_unsharded(world, cfg, use_buffers, tmp_path):
     port = _free_port()
-    mp.spawn(_worker, args=(world, port, cfg, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, cfg, str(tmp_path), use_buffers), nprocs=world, join=True)
     B, N, H, Hkv, D, w1, w2 = cfg
     q, k1, k2, v1, v2, do = so.make_inputs(B, N, H, Hkv, D, seed=7, seed_do=8)
     ref = so.forward_backward(q, k1, k2, v1, v2, do, w1, w2, 0.2)
