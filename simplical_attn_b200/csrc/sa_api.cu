@@ -179,8 +179,8 @@ int launch_fwd_tc(const sa_params* p, const KParams& k, const void* q, const voi
     DeviceInfo& dev = device_info();
     if (dev.cc_major != 10) return SA_ERR_NOT_SM100;
     CUtensorMap map_k1, map_v1;
-    if (!make_map(&map_k1, k1, k.B, k.n1, k.Hkv, k.D, k.k1, sa::tc::kColTile)) return SA_ERR_BAD_STRIDE;
-    if (!make_map(&map_v1, v1, k.B, k.n1, k.Hkv, k.D, k.v1, sa::tc::kColTile)) return SA_ERR_BAD_STRIDE;
+    if (!make_map(&map_k1, k1, k.B, k.n1, k.Hkv, k.D, k.k1, sa::tc::kSubTile)) return SA_ERR_BAD_STRIDE;
+    if (!make_map(&map_v1, v1, k.B, k.n1, k.Hkv, k.D, k.v1, sa::tc::kSubTile)) return SA_ERR_BAD_STRIDE;
     sa::tc::FwdTcParams P{};
     P.k = k;
     P.dw_log2 = dw_log2_of(k.w2);
@@ -236,6 +236,17 @@ int sa_prof_read(unsigned long long* cycles, unsigned long long* counts) {
     unsigned long long z[64] = {0};
     cudaMemcpyToSymbol(sa::ptx::g_prof_cycles, z, 64 * 8);
     cudaMemcpyToSymbol(sa::ptx::g_prof_count, z, 64 * 8);
+    return 0;
+}
+#endif
+
+#ifdef SA_TRACE
+int sa_trace_read(unsigned long long* ev, int* n) {
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(ev, sa::ptx::g_trace, sizeof(unsigned long long) * 16 * 2048);
+    cudaMemcpyFromSymbol(n, sa::ptx::g_trace_n, sizeof(int) * 16);
+    int z[16] = {0};
+    cudaMemcpyToSymbol(sa::ptx::g_trace_n, z, sizeof(z));
     return 0;
 }
 #endif

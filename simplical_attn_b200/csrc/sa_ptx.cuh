@@ -57,6 +57,25 @@ struct WaitCtx {
     uint64_t limit_ns;           // how long one wait may last before the block gives up
 };
 
+#ifdef SA_TRACE
+// Trace builds only: block 0 records (clock, event) pairs per role; read back through sa_trace_read.
+// The event counter of a role lives in a register of the recording warp (SA_TR_DECL in the scope of
+// the role's code), so that recording costs one store and no load.
+__device__ unsigned long long g_trace[16][2048];
+__device__ int g_trace_n[16];
+#define SA_TR_DECL() int tr_n_ = 0
+#define SA_TR(role, ev)                                                                           \
+    do {                                                                                          \
+        if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && tr_n_ < 2048) {                         \
+            sa::ptx::g_trace[role][tr_n_] = ((unsigned long long)clock64() << 8) | (unsigned)(ev); \
+            sa::ptx::g_trace_n[role] = ++tr_n_;                                                   \
+        }                                                                                         \
+    } while (0)
+#else
+#define SA_TR_DECL() do { } while (0)
+#define SA_TR(role, ev) do { } while (0)
+#endif
+
 #ifdef SA_PROFILE
 // Profiling builds only: cycles block 0 spent in each wait site (indexed by the site id) and how
 // often, read back through sa_prof_read.
@@ -142,6 +161,10 @@ __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.p
 
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+// Arrives without waiting: the barrier completes once `nthreads` threads have arrived or synchronised on it.
+__device__ __forceinline__ void named_barrier_arrive(int id, int nthreads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
 // ----------------------------------------------------------------------------------------------
@@ -413,40 +436,46 @@ __device__ __forceinline__ void form_product_tile(uint8_t* tile, int slab_bytes,
 // used for all the queries it pairs with: consecutive queries share all but one of their DW rows.
 // Window row w (0 <= w < DW + nq - 1) is y row  kb = i0 + halo2 - (DW-1) + w ; it meets query x at
 // delta = DW - 1 + x - w.  One round of loads per tile: NQ chunks of x and PASSES chunks of y.
+// The work is split in two so that a caller can start the loads long before it may write the tile:
+// load_product_tile_shared fills the registers, store_product_tile_shared multiplies and stores.
+template <int HD, int DWLOG, int NTHREADS = 128>
+struct ProductTileShape {
+    static constexpr int C = HD / 8;
+    static constexpr int RPP = NTHREADS / C;             // window rows per pass
+    static constexpr int DW = 1 << DWLOG;
+    static constexpr int NQ = 128 / DW;
+    static constexpr int NWIN = DW + NQ - 1;
+    static constexpr int PASSES = (NWIN + RPP - 1) / RPP;
+    static constexpr int NREGS = NQ + PASSES;            // 16-byte registers per thread
+};
+
+template <int HD, int DWLOG, int NTHREADS = 128>
+__device__ __forceinline__ void load_product_tile_shared(uint4* regs, int t, int i0, int n_q, int halo2, const __nv_bfloat16* x,
+                                                         int64_t xs, const __nv_bfloat16* y, int64_t ys) {
+    using S = ProductTileShape<HD, DWLOG, NTHREADS>;
+    const int c = t % S::C, pr = t / S::C;
+    const int kb_first = i0 + halo2 - (S::DW - 1);
+#pragma unroll
+    for (int q2 = 0; q2 < S::NQ; ++q2) {
+        regs[q2] = make_uint4(0, 0, 0, 0);
+        if (i0 + q2 < n_q) regs[q2] = __ldg((const uint4*)(x + (int64_t)(i0 + q2) * xs) + c);
+    }
+#pragma unroll
+    for (int k = 0; k < S::PASSES; ++k) {
+        const int w = pr + k * S::RPP;
+        const int kb = kb_first + w;
+        regs[S::NQ + k] = make_uint4(0, 0, 0, 0);
+        if (w < S::NWIN && kb >= 0) regs[S::NQ + k] = __ldg((const uint4*)(y + (int64_t)kb * ys) + c);
+    }
+}
+
 template <int HD, int DWLOG, bool BIAS, int NTHREADS = 128>
-__device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab_bytes, int t, int i0, int n_q, int w2,
-                                                         int halo2, const __nv_bfloat16* x, int64_t xs,
-                                                         const __nv_bfloat16* y, int64_t ys, float bias) {
-    constexpr int C = HD / 8;
-    constexpr int RPP = NTHREADS / C;             // window rows per pass
-    constexpr int DW = 1 << DWLOG;
-    constexpr int NQ = 128 / DW;
-    constexpr int NWIN = DW + NQ - 1;
-    constexpr int PASSES = (NWIN + RPP - 1) / RPP;
+__device__ __forceinline__ void store_product_tile_shared(uint8_t* tile, int slab_bytes, int t, int i0, int n_q, int w2, int halo2,
+                                                          const uint4* regs, float bias) {
+    using S = ProductTileShape<HD, DWLOG, NTHREADS>;
+    constexpr int C = S::C, RPP = S::RPP, DW = S::DW, NQ = S::NQ, PASSES = S::PASSES;
     const int c = t % C, pr = t / C;
     const int kb_first = i0 + halo2 - (DW - 1);
-    uint4 xa[NQ], ya[PASSES];
-    SA_PROF_T0(t_ld);
-#pragma unroll
-    for (int q2 = 0; q2 < NQ; ++q2) {
-        xa[q2] = make_uint4(0, 0, 0, 0);
-        if (i0 + q2 < n_q) xa[q2] = __ldg((const uint4*)(x + (int64_t)(i0 + q2) * xs) + c);
-    }
-#pragma unroll
-    for (int k = 0; k < PASSES; ++k) {
-        const int w = pr + k * RPP;
-        const int kb = kb_first + w;
-        ya[k] = make_uint4(0, 0, 0, 0);
-        if (w < NWIN && kb >= 0) ya[k] = __ldg((const uint4*)(y + (int64_t)kb * ys) + c);
-    }
-#ifdef SA_PROFILE
-#pragma unroll
-    for (int k = 0; k < PASSES; ++k) asm volatile("" ::"r"(ya[k].x), "r"(ya[k].w));
-#pragma unroll
-    for (int q2 = 0; q2 < NQ; ++q2) asm volatile("" ::"r"(xa[q2].x), "r"(xa[q2].w));
-    SA_PROF_ADD(60, t_ld);
-    SA_PROF_T0(t_st);
-#endif
     // Row r = q2 * DW + delta of the tile, delta = DW - 1 + q2 - w, w = pr + k * RPP.  DW and RPP are
     // multiples of 8, so the swizzle term (r & 7) = (q2 + 7 - pr) & 7 does not depend on the pass:
     // one base address per query, the passes are constant offsets from it.
@@ -466,10 +495,26 @@ __device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab
             bool ok = dlt < lim;
             if (BIAS) ok = ok && q_ok && (kb_first + pr + k * RPP >= 0);
             uint4 out = make_uint4(0, 0, 0, 0);
-            if (ok) out = BIAS ? mul_chunk(xa[q2], ya[k], bias) : mul_chunk_nobias(xa[q2], ya[k]);
+            if (ok) out = BIAS ? mul_chunk(regs[q2], regs[NQ + k], bias) : mul_chunk_nobias(regs[q2], regs[NQ + k]);
             *(uint4*)(bq - 128 * RPP * k) = out;
         }
     }
+}
+
+template <int HD, int DWLOG, bool BIAS, int NTHREADS = 128>
+__device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab_bytes, int t, int i0, int n_q, int w2,
+                                                         int halo2, const __nv_bfloat16* x, int64_t xs,
+                                                         const __nv_bfloat16* y, int64_t ys, float bias) {
+    uint4 regs[ProductTileShape<HD, DWLOG, NTHREADS>::NREGS];
+    SA_PROF_T0(t_ld);
+    load_product_tile_shared<HD, DWLOG, NTHREADS>(regs, t, i0, n_q, halo2, x, xs, y, ys);
+#ifdef SA_PROFILE
+#pragma unroll
+    for (int k = 0; k < ProductTileShape<HD, DWLOG, NTHREADS>::NREGS; ++k) asm volatile("" ::"r"(regs[k].x), "r"(regs[k].w));
+    SA_PROF_ADD(60, t_ld);
+    SA_PROF_T0(t_st);
+#endif
+    store_product_tile_shared<HD, DWLOG, BIAS, NTHREADS>(tile, slab_bytes, t, i0, n_q, w2, halo2, regs, bias);
 #ifdef SA_PROFILE
     SA_PROF_ADD(61, t_st);
 #endif

@@ -214,24 +214,27 @@ __device__ __forceinline__ void issue_sdp(uint32_t leader, uint32_t tm_s, uint32
                     dz + (((kk >> 2) * L::kSmallSlab + (kk & 3) * 32) >> 4), idesc, kk > 0);
 }
 
-template <int HD>
+// SPLIT: P and dS of a tile were written by two groups, each into the first 16 columns of its own 32-column half
+// of the buffer (k-steps 0, 1 at columns 0..15, k-steps 2, 3 at columns 32..47); otherwise packed at columns 0..31.
+template <int HD, bool SPLIT = false>
 __device__ __forceinline__ void issue_acc(uint32_t leader, uint32_t tm_acc1, uint32_t tm_acc2, uint32_t tm_p, uint32_t tm_ds, uint32_t w,
                                           uint32_t z, int ksteps, bool accumulate) {
     using L = BwdSmem<HD>;
     const uint32_t idesc = ptx::make_idesc(128, HD, false, true);
     const uint64_t dw = ptx::desc_mnmajor(w, L::kSmallSlab), dz = ptx::desc_mnmajor(z, L::kSmallSlab);
+    auto col = [](int kk) { return SPLIT ? (kk >> 1) * 32 + (kk & 1) * 8 : kk * 8; };
     if (ksteps == kStreamRows / 16) {
 #pragma unroll
         for (int kk = 0; kk < kStreamRows / 16; ++kk)
-            ptx::mma_ts(leader, tm_acc1, tm_p + kk * 8, dz + kk * (2048 >> 4), idesc, accumulate || kk > 0);
+            ptx::mma_ts(leader, tm_acc1, tm_p + col(kk), dz + kk * (2048 >> 4), idesc, accumulate || kk > 0);
 #pragma unroll
         for (int kk = 0; kk < kStreamRows / 16; ++kk)
-            ptx::mma_ts(leader, tm_acc2, tm_ds + kk * 8, dw + kk * (2048 >> 4), idesc, accumulate || kk > 0);
+            ptx::mma_ts(leader, tm_acc2, tm_ds + col(kk), dw + kk * (2048 >> 4), idesc, accumulate || kk > 0);
     } else {
         for (int kk = 0; kk < ksteps; ++kk)
-            ptx::mma_ts(leader, tm_acc1, tm_p + kk * 8, dz + kk * (2048 >> 4), idesc, accumulate || kk > 0);
+            ptx::mma_ts(leader, tm_acc1, tm_p + col(kk), dz + kk * (2048 >> 4), idesc, accumulate || kk > 0);
         for (int kk = 0; kk < ksteps; ++kk)
-            ptx::mma_ts(leader, tm_acc2, tm_ds + kk * 8, dw + kk * (2048 >> 4), idesc, accumulate || kk > 0);
+            ptx::mma_ts(leader, tm_acc2, tm_ds + col(kk), dw + kk * (2048 >> 4), idesc, accumulate || kk > 0);
     }
 }
 
@@ -285,6 +288,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     SA_PROF_T0(t_life);
+    SA_TR_DECL();
     if (tid == 0) {
         for (int s = 0; s < kColStages; ++s) {
             mbar_init(&st_full[s], 256);
@@ -330,6 +334,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kColTileRows;
                 const int iq0 = (int)(rho0 >> P.dw_log2);
                 mbar_wait(sdp_ready, g & 1, wctx, 20);
+                if ((warp & 3) == 0) SA_TR(1 + grp, 52);
                 tc_fence_after();
                 SA_PROF_T0(t_csm);
                 if (P.dw_log2 >= 4) {
@@ -397,6 +402,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     }
                 }
                 SA_PROF_ADD(28, t_csm);
+                if ((warp & 3) == 0) SA_TR(1 + grp, 53);
             }
             g_base += nt;
             // epilogue: group 0 writes dV1, group 1 writes dK1 (times scale)
@@ -451,6 +457,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const long rho0 = (long)(ci.tt_lo + (t % ci.ntq)) * kColTileRows;
                 uint8_t* tile = smem + L::kStream + (stage * 2 + grp) * L::kTile;
                 mbar_wait(&st_empty[stage], ((g / kColStages) & 1) ^ 1, wctx, 22);
+                if ((warp & 3) == 0) SA_TR(3 + grp, 50);
                 SA_PROF_T0(t_cform);
                 const __nv_bfloat16* xb = grp == 0 ? q + ci.b * p.q.b + h * p.q.h : d_o + ci.b * p.d_o.b + h * p.d_o.h;
                 const int64_t xs = grp == 0 ? p.q.n : p.d_o.n;
@@ -483,6 +490,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 }
                 fence_proxy_async_smem();
                 mbar_arrive(&st_full[stage]);
+                if ((warp & 3) == 0) SA_TR(3 + grp, 51);
                 SA_PROF_ADD(37 + grp, t_cform);
             };
             for (int t = 0; t < nt; ++t) form_tile(t);
@@ -510,7 +518,9 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     const uint32_t a_t = smem_base + L::kStream + stage * 2 * L::kTile, c_t = a_t + L::kTile;
                     const uint64_t d_a = desc_kmajor(a_t, 0), d_c = desc_kmajor(c_t, 0);
                     const uint64_t d_am = desc_mnmajor(a_t, L::kSlab), d_cm = desc_mnmajor(c_t, L::kSlab);
+                    SA_TR(0, 1);
                     mbar_wait(&st_full[stage], (g / kColStages) & 1, wctx, 25);
+                    SA_TR(0, 2);
                     tc_fence_after();
                     // S^T = K1 A^T,  dP^T = V1 C^T
                     SA_PROF_T0(t_ci1);
@@ -525,6 +535,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         mma_ss(leader, tm_dp, d_v1 + off, d_c + off, idesc_sd, kk > 0);
                     }
                     tc_commit(leader, sdp_ready);
+                    SA_TR(0, 3);
                     SA_PROF_ADD(29, t_ci1);
                     SA_PROF_T0(t_ci2);
                     // dV1 += P^T-tile C-tile,  dK1 += dS^T-tile A-tile   (K = 128 virtual rows: 8 steps of 16).
@@ -532,6 +543,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
                         mbar_wait(&pds_ready[k], g & 1, wctx, 26);
+                        SA_TR(0, 10 + k);
                         tc_fence_after();
 #pragma unroll
                         for (int gq = 0; gq < 2; ++gq) {
@@ -545,6 +557,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         }
                     }
                     tc_commit(leader, &st_empty[stage]);
+                    SA_TR(0, 4);
                     SA_PROF_ADD(36, t_ci2);
                 }
                 tc_commit(leader, acc_ready);
@@ -681,6 +694,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     SA_PROF_T0(t_life);
+    SA_TR_DECL();
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&B.st_full[s], 1);
@@ -1099,7 +1113,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 //     the epilogue of a unit overlaps the main loop of the next one.  Same math, same order of
 //     additions, same workspace contents as bwd_row_kernel.
 // ------------------------------------------------------------------------------------------------
-constexpr int kRow2Threads = 640;     // softmax groups (0-7), epilogue groups (8-15), MMA (16), TMA (17), 2 idle
+constexpr int kRow2Threads = 640;     // softmax groups (0-7), epilogue groups (8-15), MMA issuers (16, 17), TMA (18), 1 idle
 
 template <int HD, int DWL, int NS, bool BIAS>
 __global__ void __launch_bounds__(kRow2Threads, 1)
@@ -1120,25 +1134,30 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
     const uint32_t smem_base = smem_u32(smem);
     const KParams& p = P.k;
     const BwdBars B = bwd_bars<NS>((uint64_t*)(smem + L::kBars));
+    uint64_t* const buf_free = (uint64_t*)(smem + L::kBars) + 2 * NS + 8;      // [2] an S / dP buffer's P and dS have been consumed
     uint32_t* tmem_slot = (uint32_t*)(smem + L::kMisc);
     volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
     const WaitCtx wctx{abort_flag, P.status, P.wait_limit_ns};
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     SA_PROF_T0(t_life);
+    SA_TR_DECL();
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&B.st_full[s], 1);
             mbar_init(&B.st_empty[s], 1);
         }
+        // (barriers a warp group arrives on count one elected arrival per warp)
         for (int b = 0; b < 2; ++b) {
             mbar_init(&B.sdp_ready[b], 1);
-            mbar_init(&B.pds_ready[b], 128);
+            mbar_init(&B.pds_ready[b], 8);     // both softmax groups: each turns half the columns of a tile into P and dS
         }
-        mbar_init(B.stat_full, 256);       // A and C formed by the two softmax groups
+        mbar_init(B.stat_full, 8);         // A and C formed by the two softmax groups
         mbar_init(B.stat_empty, 1);        // the unit's last S / dP MMAs have read A and C
         mbar_init(B.acc_ready, 1);         // U and G final
-        mbar_init(B.acc_free, 256);        // U and G read out by the two epilogue groups
+        mbar_init(B.acc_free, 8);          // U and G read out by the two epilogue groups
+        mbar_init(&buf_free[0], 1);
+        mbar_init(&buf_free[1], 1);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -1158,6 +1177,10 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
     // rest): an increase beyond the block's own pool would never return.
     if (warp < 8) {
         // ---------------------------------------------------------------- operand formation + softmax
+        // Group 0 forms A = Q * K2, group 1 forms C = dO * V2.  Every column tile (64 columns) is split
+        // between the groups: group g turns columns [32g, 32g + 32) of S and dP into P and dS, so a tile's
+        // softmax takes half as long and the accumulating MMAs that wait for it start that much earlier.
+        // P and dS (bf16) go to columns [32g, 32g + 16) of the S / dP buffer: inside the group's own columns.
         reg_alloc<120>();
         const int grp = warp >> 2;
         const int row = tid & 127;
@@ -1166,62 +1189,84 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         const int dlt = row & (DW - 1);
         const float c2 = p.scale * kLog2e;
         uint8_t* my_tile = smem + (grp == 0 ? L::kStat0 : L::kStat1);      // group 0 forms A, group 1 forms C
-        uint32_t n_mine = 0, n_units = 0;
-        for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
-            const RowItem ri = row_item(P, it);
-            for (int i0 = ri.i_run0; i0 < ri.i_run1; i0 += QPT, ++n_units) {
-                const RowUnit ru = row_unit(P, i0);
-                const int i = i0 + qq;
-                const int kb = i + p.halo2 - dlt;
-                const bool row_valid = (i < p.N) && (dlt < p.w2) && (kb >= 0);
-                const int ic = min(i, p.N - 1);
-                // ---- stationary operand of this group, once the previous unit's S / dP MMAs have read the old one
-                if (n_units > 0) mbar_wait(B.stat_empty, (n_units - 1) & 1, wctx, 37);
-                SA_PROF_T0(t_form);
-                if (grp == 0)
-                    form_product_tile_shared<HD, DWL, BIAS>(my_tile, L::kBigSlab, row, i0, p.N, p.w2, p.halo2,
-                                                            q + ri.b * p.q.b + ri.h * p.q.h, p.q.n,
-                                                            k2 + ri.b * p.k2.b + ri.hk * p.k2.h, p.k2.n, BIAS ? p.k2_bias : 0.f);
-                else
-                    form_product_tile_shared<HD, DWL, BIAS>(my_tile, L::kBigSlab, row, i0, p.N, p.w2, p.halo2,
-                                                            d_o + ri.b * p.d_o.b + ri.h * p.d_o.h, p.d_o.n,
-                                                            v2 + ri.b * p.v2.b + ri.hk * p.v2.h, p.v2.n, BIAS ? p.v2_bias : 0.f);
-                fence_proxy_async_smem();
-                tc_fence_before();
-                mbar_arrive(B.stat_full);
-                SA_PROF_ADD(40 + grp, t_form);
-                SA_PROF_T0(t_loop);
-                const long li = ((long)ri.b * p.H + ri.h) * p.N + ic;
-                const float lse2 = P.lse2[li], dlt_i = P.delta[li];
-                const int jhi = row_valid ? i + p.halo1 : -1;
-                const int jlo = row_valid ? max(0, i + p.halo1 - p.w1 + 1) : 0;
-                // ---- column tiles of this group
-                for (int t = grp; t < ru.nt; t += 2, ++n_mine) {
-                    const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
-                    const int tile0 = ru.col_start + t * kStreamRows;
-                    const int lo = jlo - tile0, hi = jhi - tile0;
-                    const bool full = __all_sync(0xffffffffu, lo <= 0 && hi >= kStreamRows - 1);
-                    mbar_wait(&B.sdp_ready[grp], n_mine & 1, wctx, 30);
-                    tc_fence_after();
-                    SA_PROF_T0(t_rsm);
-#pragma unroll 1
-                    for (int c0 = 0; c0 < width; c0 += 32) {
-                        uint32_t s[32], dp[32], pp[16], ds[16];
-                        tmem_ld32(tm_s[grp] + lane_addr + c0, s);
-                        tmem_ld32(tm_dp[grp] + lane_addr + c0, dp);
-                        tmem_wait_ld();
-                        if (full) softmax_bwd_chunk<false>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
-                        else softmax_bwd_chunk<true>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
-                        tmem_st16(tm_s[grp] + lane_addr + (c0 >> 1), pp);
-                        tmem_st16(tm_dp[grp] + lane_addr + (c0 >> 1), ds);
-                    }
+        auto warp_arrive = [&](uint64_t* bar) {      // every lane has finished and fenced its part; lane 0 arrives for the warp
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar);
+        };
+        const __nv_bfloat16* const x_t = grp == 0 ? q : d_o;               // row operand of this group's tile
+        const __nv_bfloat16* const y_t = grp == 0 ? k2 : v2;               // window operand
+        const sa_strides xs = grp == 0 ? p.q : p.d_o, ys = grp == 0 ? p.k2 : p.v2;
+        const float bias = BIAS ? (grp == 0 ? p.k2_bias : p.v2_bias) : 0.f;
+        uint4 fr[ProductTileShape<HD, DWL>::NREGS];  // the unit's operand rows, loaded one unit ahead
+        uint32_t nb[2] = {0, 0}, n_units = 0;
+        long it = blockIdx.x;
+        RowItem ri = row_item(P, it < P.num_row_items ? it : 0);
+        int i0 = ri.i_run0;
+        if (it < P.num_row_items)
+            load_product_tile_shared<HD, DWL>(fr, row, i0, p.N, p.halo2, x_t + ri.b * xs.b + ri.h * xs.h, xs.n,
+                                              y_t + ri.b * ys.b + ri.hk * ys.h, ys.n);
+        while (it < P.num_row_items) {
+            const RowUnit ru = row_unit(P, i0);
+            const int i = i0 + qq;
+            const int kb = i + p.halo2 - dlt;
+            const bool row_valid = (i < p.N) && (dlt < p.w2) && (kb >= 0);
+            const int ic = min(i, p.N - 1);
+            // ---- stationary operand of this group, once the previous unit's S / dP MMAs have read the old one
+            if (n_units > 0) mbar_wait(B.stat_empty, (n_units - 1) & 1, wctx, 37);
+            if ((warp & 3) == 0) SA_TR(1 + grp, 50);
+            SA_PROF_T0(t_form);
+            store_product_tile_shared<HD, DWL, BIAS>(my_tile, L::kBigSlab, row, i0, p.N, p.w2, p.halo2, fr, bias);
+            fence_proxy_async_smem();
+            tc_fence_before();
+            warp_arrive(B.stat_full);
+            if ((warp & 3) == 0) SA_TR(1 + grp, 51);
+            SA_PROF_ADD(40 + grp, t_form);
+            SA_PROF_T0(t_loop);
+            const long li = ((long)ri.b * p.H + ri.h) * p.N + ic;
+            const float lse2 = P.lse2[li], dlt_i = P.delta[li];
+            const int jhi = row_valid ? i + p.halo1 : -1;
+            const int jlo = row_valid ? max(0, i + p.halo1 - p.w1 + 1) : 0;
+            // ---- this group's half of every column tile
+            for (int t = 0; t < ru.nt; ++t) {
+                const int b = t & 1;
+                const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
+                const int c0 = 32 * grp;                                   // first column of this group's half
+                const int tile0 = ru.col_start + t * kStreamRows;
+                const int lo = jlo - tile0, hi = jhi - tile0;
+                const bool full = __all_sync(0xffffffffu, lo <= c0 && hi >= c0 + 31);
+                mbar_wait(&B.sdp_ready[b], nb[b] & 1, wctx, 30);
+                ++nb[b];
+                if ((warp & 3) == 0) SA_TR(1 + grp, 52);
+                tc_fence_after();
+                SA_PROF_T0(t_rsm);
+                if (c0 < width) {
+                    uint32_t s[32], dp[32], pp[16], ds[16];
+                    tmem_ld32(tm_s[b] + lane_addr + c0, s);
+                    tmem_ld32(tm_dp[b] + lane_addr + c0, dp);
+                    tmem_wait_ld();
+                    if (full) softmax_bwd_chunk<false>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
+                    else softmax_bwd_chunk<true>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
+                    tmem_st16(tm_s[b] + lane_addr + c0, pp);
+                    tmem_st16(tm_dp[b] + lane_addr + c0, ds);
                     tmem_wait_st();
-                    tc_fence_before();
-                    mbar_arrive(&B.pds_ready[grp]);
-                    SA_PROF_ADD(58 + grp, t_rsm);
                 }
-                SA_PROF_ADD(42 + grp, t_loop);
+                tc_fence_before();
+                warp_arrive(&B.pds_ready[b]);
+                if ((warp & 3) == 0) SA_TR(1 + grp, 53);
+                SA_PROF_ADD(58 + grp, t_rsm);
             }
+            SA_PROF_ADD(42 + grp, t_loop);
+            // ---- next unit; its operand rows start travelling now (always some unit's rows, so that the registers
+            // are defined on every path)
+            ++n_units;
+            i0 += QPT;
+            if (i0 >= ri.i_run1) {
+                it += gridDim.x;
+                ri = row_item(P, it < P.num_row_items ? it : it - gridDim.x);
+                i0 = ri.i_run0;
+            }
+            load_product_tile_shared<HD, DWL>(fr, row, i0, p.N, p.halo2, x_t + ri.b * xs.b + ri.h * xs.h, xs.n,
+                                              y_t + ri.b * ys.b + ri.hk * ys.h, ys.n);
         }
     } else if (warp < 16) {
         // ---------------------------------------------------------------- epilogue groups: group g takes columns
@@ -1268,6 +1313,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                 const int slot = row_valid ? kb % max(ring_rows, 1) : 0;
                 __nv_bfloat16* dq_out = dq == nullptr ? nullptr : dq + ri.b * p.dq.b + (long)i0 * p.dq.n + ri.h * p.dq.h + cbase;
                 mbar_wait(B.acc_ready, n_units & 1, wctx, 31);
+                if ((warp & 3) == 0) SA_TR(3 + grp, 60);
                 tc_fence_after();
                 SA_PROF_T0(t_epi);
                 // A warp holds the 32 deltas of one query (or the 16 deltas of two): within a query the lanes own distinct K2 rows.  Warp w works
@@ -1327,10 +1373,12 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                         if (TWO_Q) __syncwarp();
                     }
                     named_barrier_sync(3 + grp, 128);
+                    if ((warp & 3) == 0) SA_TR(3 + grp, 61 + ph);
                 }
                 // U / G have been read: the next unit's accumulating MMAs may start
                 tc_fence_before();
-                mbar_arrive(B.acc_free);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(B.acc_free);
                 if (WPQ > 1 && dq != nullptr) {
                     // a query spans WPQ warps: add their partial rows (the last phase ended with a barrier)
                     for (int idx = row; idx < QPT * HALF; idx += 128) {
@@ -1368,57 +1416,84 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                     named_barrier_sync(3 + grp, 128);     // cleared slots are visible before the next unit's updates
                 }
                 SA_PROF_ADD(44 + grp, t_epi);
+                if ((warp & 3) == 0) SA_TR(3 + grp, 66);
             }
         }
     } else if (warp == 16) {
-        // ---------------------------------------------------------------- MMA issuer
+        // ---------------------------------------------------------------- MMA issuer of the S / dP tiles.  Two warps
+        // issue MMAs: this one S and dP, warp 17 the accumulating U and G.  One warp alone spends as long on the
+        // scalar work between two batches (barriers, descriptors) as the tensor cores need for a batch, and its
+        // issue queue is short, so the tensor cores would idle through that work; with two issuers one is always
+        // queued up.  The only order the two must keep is on an S / dP buffer: tile t + 2 overwrites what the
+        // accumulating MMAs of tile t read (buf_free, completed by the tensor cores themselves).
         reg_dealloc<48>();
         {
             const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
-            uint32_t nb[2] = {0, 0}, g_base = 0, n_units = 0;
+            uint32_t nbf[2] = {0, 0}, g_base = 0, n_units = 0;
             const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false);
             const uint32_t a_s = smem_base + L::kStat0, c_s = smem_base + L::kStat1;
             for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
                 const RowItem ri = row_item(P, it);
                 for (int i0 = ri.i_run0; i0 < ri.i_run1; i0 += QPT, ++n_units) {
                     const RowUnit ru = row_unit(P, i0);
+                    SA_TR(0, 1);
                     mbar_wait(B.stat_full, n_units & 1, wctx, 32);      // A, C formed
+                    SA_TR(0, 2);
                     tc_fence_after();
-                    for (int t = 0; t <= ru.nt; ++t) {
-                        if (t < ru.nt) {
-                            const uint32_t g = g_base + t;
-                            const int stage = (int)(g % NS), b = t & 1;
-                            const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
-                            const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
-                            mbar_wait(&B.st_full[stage], (g / NS) & 1, wctx, 33);
-                            tc_fence_after();
-                            issue_sdp<HD>(leader, tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false));
-                            tc_commit(leader, &B.sdp_ready[b]);
-                            if (t == ru.nt - 1) tc_commit(leader, B.stat_empty);     // A and C may be overwritten
-                        }
-                        if (t >= 1) {
-                            const int tp = t - 1;
-                            const uint32_t g = g_base + tp;
-                            const int stage = (int)(g % NS), b = tp & 1;
-                            const int width = (tp == ru.nt - 1) ? ru.last_width : kStreamRows;
-                            const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
-                            mbar_wait(&B.pds_ready[b], nb[b] & 1, wctx, 34);
-                            ++nb[b];
-                            // the previous unit's U and G have been read out by the epilogue groups
-                            if (tp == 0 && n_units > 0) mbar_wait(B.acc_free, (n_units - 1) & 1, wctx, 38);
-                            tc_fence_after();
-                            // U += P V1-tile ; G += dS K1-tile
-                            issue_acc<HD>(leader, tm_u, tm_g, tm_s[b], tm_dp[b], k1_t, v1_t, width / 16, tp > 0);
-                            tc_commit(leader, &B.st_empty[stage]);
-                        }
+                    for (int t = 0; t < ru.nt; ++t) {
+                        const uint32_t g = g_base + t;
+                        const int stage = (int)(g % NS), b = t & 1;
+                        const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
+                        const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
+                        mbar_wait(&B.st_full[stage], (g / NS) & 1, wctx, 33);
+                        // the accumulating MMAs of the tile that used this buffer before have read its P and dS
+                        if (nbf[b] > 0) mbar_wait(&buf_free[b], (nbf[b] - 1) & 1, wctx, 39);
+                        SA_TR(0, 3);
+                        tc_fence_after();
+                        issue_sdp<HD>(leader, tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false));
+                        tc_commit(leader, &B.sdp_ready[b]);
+                        if (t == ru.nt - 1) tc_commit(leader, B.stat_empty);     // A and C may be overwritten
+                        ++nbf[b];
+                        SA_TR(0, 4);
                     }
-                    tc_commit(leader, B.acc_ready);
                     g_base += ru.nt;
                 }
             }
         }
         __syncwarp();
     } else if (warp == 17) {
+        // ---------------------------------------------------------------- MMA issuer of the accumulating U and G
+        reg_dealloc<48>();
+        {
+            const uint32_t leader = elect_one();
+            uint32_t nb[2] = {0, 0}, g_base = 0, n_units = 0;
+            for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
+                const RowItem ri = row_item(P, it);
+                for (int i0 = ri.i_run0; i0 < ri.i_run1; i0 += QPT, ++n_units) {
+                    const RowUnit ru = row_unit(P, i0);
+                    for (int tp = 0; tp < ru.nt; ++tp) {
+                        const uint32_t g = g_base + tp;
+                        const int stage = (int)(g % NS), b = tp & 1;
+                        const int width = (tp == ru.nt - 1) ? ru.last_width : kStreamRows;
+                        const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
+                        mbar_wait(&B.pds_ready[b], nb[b] & 1, wctx, 34);
+                        SA_TR(5, 5);
+                        ++nb[b];
+                        // the previous unit's U and G have been read out by the epilogue groups
+                        if (tp == 0 && n_units > 0) { mbar_wait(B.acc_free, (n_units - 1) & 1, wctx, 38); SA_TR(5, 6); }
+                        tc_fence_after();
+                        // U += P V1-tile ; G += dS K1-tile
+                        issue_acc<HD, true>(leader, tm_u, tm_g, tm_s[b], tm_dp[b], k1_t, v1_t, width / 16, tp > 0);
+                        tc_commit(leader, &buf_free[b]);
+                        tc_commit(leader, &B.st_empty[stage]);
+                        SA_TR(5, 7);
+                    }
+                    tc_commit(leader, B.acc_ready);
+                    g_base += ru.nt;
+                }
+            }
+        }
+    } else if (warp == 18) {
         // ---------------------------------------------------------------- TMA: streamed K1 / V1 tiles
         reg_dealloc<48>();
         if (lane == 0) {
