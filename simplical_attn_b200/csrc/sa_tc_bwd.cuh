@@ -79,7 +79,7 @@ struct BwdSmem {
     static constexpr int kStream = 2 * kBigTile;             // NS x (tile0 | tile1)
     static constexpr int kMeta = kStream + NS * 2 * kSmallTile;   // per stage: 64 lse2 + 64 delta
     static constexpr int kBars = kMeta + NS * 128 * 4;
-    static constexpr int kNumBars = 2 * NS + 10;
+    static constexpr int kNumBars = 2 * NS + 14;
     static constexpr int kMisc = kBars + kNumBars * 8;
     static constexpr int kTotal = kMisc + 16;
     static constexpr int kRing = kTotal;                     // row kernel: 2 x ring_rows x HD floats (optional)
@@ -1113,6 +1113,13 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 //     the epilogue of a unit overlaps the main loop of the next one.  Same math, same order of
 //     additions, same workspace contents as bwd_row_kernel.
 // ------------------------------------------------------------------------------------------------
+// Bytes of one staging buffer of the row kernel with separate epilogue warpgroups: the raw Q and dO rows of a
+// unit's queries and the K2 rows of their window (row pitch padded by 16 bytes so that the lanes of a warp, which
+// read consecutive rows at the same column, fall into different banks).  Used for 16 and 32 delta slots per query.
+constexpr int row2_stage_bytes(int dwl, int hd) {
+    return dwl > 5 ? 0 : 2 * (128 >> dwl) * hd * 2 + ((1 << dwl) + (128 >> dwl) - 1) * (hd * 2 + 16);
+}
+
 constexpr int kRow2Threads = 640;     // softmax groups (0-7), epilogue groups (8-15), MMA issuers (16, 17), TMA (18), 1 idle
 
 template <int HD, int DWL, int NS, bool BIAS>
@@ -1135,6 +1142,16 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
     const KParams& p = P.k;
     const BwdBars B = bwd_bars<NS>((uint64_t*)(smem + L::kBars));
     uint64_t* const buf_free = (uint64_t*)(smem + L::kBars) + 2 * NS + 8;      // [2] an S / dP buffer's P and dS have been consumed
+    uint64_t* const stg_full = buf_free + 2;                                  // [2] staging buffer written (softmax groups -> epilogue groups)
+    uint64_t* const stg_free = buf_free + 4;                                  // [2] staging buffer read (epilogue groups -> softmax groups)
+    // Staging: the softmax groups have a unit's Q, dO and K2 rows in registers when they form A and C; they leave
+    // raw copies in shared memory for the epilogue groups, which would otherwise fetch the same rows from global
+    // memory in every phase, with the latency of those loads on the path that frees the accumulators.
+    constexpr bool STAGE = DWL <= 5;
+    constexpr int NWIN = DW + QPT - 1;
+    constexpr int K2PITCH = HD * 2 + 16;
+    constexpr int kStageBuf = row2_stage_bytes(DWL, HD);
+    uint8_t* const stage_base = smem + L::kRing + 2 * ring_rows * (HD + 2) * 4 + 2048;      // behind the rings and the partial dQ rows
     uint32_t* tmem_slot = (uint32_t*)(smem + L::kMisc);
     volatile int* abort_flag = (volatile int*)(smem + L::kMisc + 4);
     const WaitCtx wctx{abort_flag, P.status, P.wait_limit_ns};
@@ -1156,8 +1173,11 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         mbar_init(B.stat_empty, 1);        // the unit's last S / dP MMAs have read A and C
         mbar_init(B.acc_ready, 1);         // U and G final
         mbar_init(B.acc_free, 8);          // U and G read out by the two epilogue groups
-        mbar_init(&buf_free[0], 1);
-        mbar_init(&buf_free[1], 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&buf_free[b], 1);
+            mbar_init(&stg_full[b], 8);
+            mbar_init(&stg_free[b], 8);
+        }
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -1216,6 +1236,25 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
             if ((warp & 3) == 0) SA_TR(1 + grp, 50);
             SA_PROF_T0(t_form);
             store_product_tile_shared<HD, DWL, BIAS>(my_tile, L::kBigSlab, row, i0, p.N, p.w2, p.halo2, fr, bias);
+            if constexpr (STAGE) {
+                using S = ProductTileShape<HD, DWL>;
+                const int sb = n_units & 1;                              // this unit's staging buffer; its (n_units >> 1)-th use
+                if (n_units >= 2) mbar_wait(&stg_free[sb], ((n_units >> 1) - 1) & 1, wctx, 40);
+                uint8_t* const stg = stage_base + sb * kStageBuf;
+                const int c = row % S::C, pr = row / S::C;
+                if (pr == 0) {                                           // Q rows (group 0) / dO rows (group 1)
+#pragma unroll
+                    for (int q2 = 0; q2 < S::NQ; ++q2) *(uint4*)(stg + (grp * QPT + q2) * HD * 2 + c * 16) = fr[q2];
+                }
+                if (grp == 0) {                                          // the K2 rows of the unit's window
+#pragma unroll
+                    for (int k = 0; k < S::PASSES; ++k) {
+                        const int w = pr + k * S::RPP;
+                        if (w < NWIN) *(uint4*)(stg + 2 * QPT * HD * 2 + w * K2PITCH + c * 16) = fr[S::NQ + k];
+                    }
+                }
+                warp_arrive(&stg_full[sb]);
+            }
             fence_proxy_async_smem();
             tc_fence_before();
             warp_arrive(B.stat_full);
@@ -1312,6 +1351,13 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                 if (uidx == 0) flush_lo = max(0, own0 - (p.w2 - 1));
                 const int slot = row_valid ? kb % max(ring_rows, 1) : 0;
                 __nv_bfloat16* dq_out = dq == nullptr ? nullptr : dq + ri.b * p.dq.b + (long)i0 * p.dq.n + ri.h * p.dq.h + cbase;
+                const uint8_t* stg = nullptr;
+                if constexpr (STAGE) {
+                    const int sb = n_units & 1;
+                    mbar_wait(&stg_full[sb], (n_units >> 1) & 1, wctx, 41);
+                    stg = stage_base + sb * kStageBuf;
+                }
+                const int wrow_k2 = qq + DW - 1 - dlt;                       // this lane's K2 row inside the unit's window
                 mbar_wait(B.acc_ready, n_units & 1, wctx, 31);
                 if ((warp & 3) == 0) SA_TR(3 + grp, 60);
                 tc_fence_after();
@@ -1324,9 +1370,15 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                 for (int ph = 0; ph < NPHG; ++ph) {
                     const int c = ((wq + ph) & 3) * CW;
                     uint32_t qw[CW / 2], ow[CW / 2], xw[CW / 2], g[CW], u[CW];
-                    load_bf16_words<CW>(q_row + c, qw);
-                    load_bf16_words<CW>(do_row + c, ow);
-                    load_bf16_words<CW>(k2_row + c, xw);
+                    if constexpr (STAGE) {
+                        load_bf16_words<CW>((const __nv_bfloat16*)(stg + qq * HD * 2) + cbase + c, qw);
+                        load_bf16_words<CW>((const __nv_bfloat16*)(stg + (QPT + qq) * HD * 2) + cbase + c, ow);
+                        load_bf16_words<CW>((const __nv_bfloat16*)(stg + 2 * QPT * HD * 2 + wrow_k2 * K2PITCH) + cbase + c, xw);
+                    } else {
+                        load_bf16_words<CW>(q_row + c, qw);
+                        load_bf16_words<CW>(do_row + c, ow);
+                        load_bf16_words<CW>(k2_row + c, xw);
+                    }
                     tmem_ld16(tm_g + lane_addr + cbase + c, g);
                     tmem_ld16(tm_u + lane_addr + cbase + c, u);
                     tmem_wait_ld();
@@ -1378,7 +1430,10 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                 // U / G have been read: the next unit's accumulating MMAs may start
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(B.acc_free);
+                if (lane == 0) {
+                    mbar_arrive(B.acc_free);
+                    if constexpr (STAGE) mbar_arrive(&stg_free[n_units & 1]);      // ... and the staging buffer may be rewritten
+                }
                 if (WPQ > 1 && dq != nullptr) {
                     // a query spans WPQ warps: add their partial rows (the last phase ended with a barrier)
                     for (int idx = row; idx < QPT * HALF; idx += 128) {
@@ -1703,12 +1758,16 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
             constexpr int kDqPart = 2048;     // partial dQ rows of the epilogue groups when a query spans two warps
             const bool fits2 = L2::kRing + 1024 + 2 * ring_want * 130 * 4 + kDqPart <= L2::kMaxDynamic;
             const bool fits3x = L3::kRing + 1024 + 2 * ring_want * 130 * 4 + kDqPart <= L3::kMaxDynamic;
-            if (pl.dw_log2 == 5 && (fits3x || !need_kv2))     // separate epilogue warpgroups
+            // (16 and 32 delta slots: two staging buffers of raw Q, dO and K2 rows behind the rings)
+            const int stage5 = 2 * row2_stage_bytes(5, 128), stage4 = 2 * row2_stage_bytes(4, 128);
+            const bool fits5 = L3::kRing + 1024 + 2 * ring_want * 130 * 4 + kDqPart + stage5 <= L3::kMaxDynamic;
+            const bool fits4 = L3::kRing + 1024 + 2 * ring_want * 130 * 4 + kDqPart + stage4 <= L3::kMaxDynamic;
+            if (pl.dw_log2 == 5 && (fits5 || !need_kv2))     // separate epilogue warpgroups
                 ok = launch_row(has_bias ? bwd_row2_kernel<128, 5, 3, true> : bwd_row2_kernel<128, 5, 3, false>, L3::kRing, L3::kAlloc,
-                                L3::kMaxDynamic, 128, kRow2Threads, kDqPart);
-            else if (pl.dw_log2 == 4 && (fits3x || !need_kv2))
+                                L3::kMaxDynamic, 128, kRow2Threads, kDqPart + stage5);
+            else if (pl.dw_log2 == 4 && (fits4 || !need_kv2))
                 ok = launch_row(has_bias ? bwd_row2_kernel<128, 4, 3, true> : bwd_row2_kernel<128, 4, 3, false>, L3::kRing, L3::kAlloc,
-                                L3::kMaxDynamic, 128, kRow2Threads, kDqPart);
+                                L3::kMaxDynamic, 128, kRow2Threads, kDqPart + stage4);
             else if (pl.dw_log2 == 6 && (fits3x || !need_kv2))
                 ok = launch_row(has_bias ? bwd_row2_kernel<128, 6, 3, true> : bwd_row2_kernel<128, 6, 3, false>, L3::kRing, L3::kAlloc,
                                 L3::kMaxDynamic, 128, kRow2Threads, kDqPart);
