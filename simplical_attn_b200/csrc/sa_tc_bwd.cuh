@@ -291,15 +291,15 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     SA_TR_DECL();
     if (tid == 0) {
         for (int s = 0; s < kColStages; ++s) {
-            mbar_init(&st_full[s], 256);
+            mbar_init(&st_full[s], 8);         // one arrival per producer warp
             mbar_init(&st_empty[s], 1);
         }
         mbar_init(sdp_ready, 1);
-        for (int k = 0; k < 4; ++k) mbar_init(&pds_ready[k], 256);
+        for (int k = 0; k < 4; ++k) mbar_init(&pds_ready[k], 8);      // one arrival per softmax warp
         mbar_init(stat_full, 1);
         mbar_init(stat_empty, 1);
         mbar_init(acc_ready, 1);
-        mbar_init(acc_free, 256);
+        mbar_init(acc_free, 8);
         *abort_flag = 0;
         fence_mbar_init();
     }
@@ -312,6 +312,10 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tm_s = tmem_base, tm_dp = tmem_base + 128, tm_dv1 = tmem_base + 256, tm_dk1 = tmem_base + 384;
+    auto warp_arrive = [&](uint64_t* bar) {      // every lane has finished and fenced its part; lane 0 arrives for the warp
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar);
+    };
 
     if (warp < 8) {
         // ---------------------------------------------------------------- softmax groups + epilogue
@@ -367,7 +371,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             // the accumulating MMAs of this chunk start while the next one is processed
                             tmem_wait_st();
                             tc_fence_before();
-                            mbar_arrive(&pds_ready[k]);
+                            warp_arrive(&pds_ready[k]);
                         }
                     };
                     if (step_full) run_step(std::false_type{});
@@ -398,7 +402,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         tmem_st8(tm_dp + lane_addr + 64 * grp + (cc >> 1), ds);
                         tmem_wait_st();
                         tc_fence_before();
-                        mbar_arrive(&pds_ready[cc >> 4]);
+                        warp_arrive(&pds_ready[cc >> 4]);
                     }
                 }
                 SA_PROF_ADD(28, t_csm);
@@ -437,7 +441,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
             }
             if (nt > 0) {
                 tc_fence_before();
-                mbar_arrive(acc_free);
+                warp_arrive(acc_free);
             }
         }
     } else if (warp < 16) {
@@ -445,12 +449,42 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         reg_alloc<112>();
         const int grp = (warp - 8) >> 2;
         const int row = tid & 127;
+        // DWL: compile-time log2 of the delta slots per query for 16, 32 and 64 slots (the operand rows of a tile are
+        // then loaded one tile ahead, into registers, and multiplied and stored once the stage is free); 0: any other
+        // count (those load when they store).
+        auto producer_body = [&](auto dwl_c) {
+        constexpr int DWL = decltype(dwl_c)::value;
+        constexpr int kFormRegs = DWL != 0 ? ProductTileShape<HD, DWL != 0 ? DWL : 5>::NREGS : 1;
+        uint4 fr[kFormRegs];
+        float meta_lse = INFINITY, meta_delta = 0.f;
         uint32_t g_base = 0;
+        const int nq = max(1, kColTileRows >> P.dw_log2);
+        const bool meta_thread = grp == 0 && row < nq;
+        // loads of tile t of item ci (rows of Q / dO and of K2 / V2, and the LSE2 / Delta of the tile's queries)
+#define SA_COL_LOAD(CI, T)                                                                                                \
+        {                                                                                                                 \
+            const int h_ = (CI).hk * p.G + (T) / (CI).ntq;                                                                \
+            const long rho0_ = (long)((CI).tt_lo + ((T) % (CI).ntq)) * kColTileRows;                                      \
+            const int iq0_ = (int)(rho0_ >> P.dw_log2);                                                                   \
+            if constexpr (DWL != 0) {                                                                                     \
+                const __nv_bfloat16* xb_ = grp == 0 ? q + (CI).b * p.q.b + h_ * p.q.h : d_o + (CI).b * p.d_o.b + h_ * p.d_o.h; \
+                const __nv_bfloat16* yb_ = grp == 0 ? k2 + (CI).b * p.k2.b + (CI).hk * p.k2.h : v2 + (CI).b * p.v2.b + (CI).hk * p.v2.h; \
+                load_product_tile_shared<HD, DWL>(fr, row, iq0_, p.N, p.halo2, xb_, grp == 0 ? p.q.n : p.d_o.n, yb_,      \
+                                                  grp == 0 ? p.k2.n : p.v2.n);                                            \
+            }                                                                                                             \
+            meta_lse = INFINITY;                                                                                          \
+            meta_delta = 0.f;                                                                                             \
+            if (meta_thread && iq0_ + row < p.N) {                                                                        \
+                const long li_ = ((long)(CI).b * p.H + h_) * p.N + iq0_ + row;                                            \
+                meta_lse = P.lse2[li_];                                                                                   \
+                meta_delta = P.delta[li_];                                                                                \
+            }                                                                                                             \
+        }
         for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
             const ColItem ci = col_item(P, it);
             const int nt = ci.ntq * p.G;
-            // group 0 forms A = Q * (K2 + bias), group 1 forms C = dO * (V2 + bias) of a streamed tile
-            auto form_tile = [&](int t) {
+            if (nt > 0) SA_COL_LOAD(ci, 0);
+            for (int t = 0; t < nt; ++t) {
                 const uint32_t g = g_base + t;
                 const int stage = (int)(g % kColStages);
                 const int h = ci.hk * p.G + t / ci.ntq;
@@ -459,42 +493,41 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 mbar_wait(&st_empty[stage], ((g / kColStages) & 1) ^ 1, wctx, 22);
                 if ((warp & 3) == 0) SA_TR(3 + grp, 50);
                 SA_PROF_T0(t_cform);
-                const __nv_bfloat16* xb = grp == 0 ? q + ci.b * p.q.b + h * p.q.h : d_o + ci.b * p.d_o.b + h * p.d_o.h;
-                const int64_t xs = grp == 0 ? p.q.n : p.d_o.n;
-                const __nv_bfloat16* yb = grp == 0 ? k2 + ci.b * p.k2.b + ci.hk * p.k2.h : v2 + ci.b * p.v2.b + ci.hk * p.v2.h;
-                const int64_t ys = grp == 0 ? p.k2.n : p.v2.n;
                 const float bias = BIAS ? (grp == 0 ? p.k2_bias : p.v2_bias) : 0.f;
                 const int iq0 = (int)(rho0 >> P.dw_log2);
-                // LSE2 and Delta of the tile's queries: loaded before the tile is formed so that the
-                // latency of these few loads is not added behind it
-                const int nq = max(1, kColTileRows >> P.dw_log2);
-                const bool has_meta = grp == 0 && row < nq;
-                float meta_lse = INFINITY, meta_delta = 0.f;
-                if (has_meta && iq0 + row < p.N) {
-                    const long li = ((long)ci.b * p.H + h) * p.N + iq0 + row;
-                    meta_lse = P.lse2[li];
-                    meta_delta = P.delta[li];
+                if constexpr (DWL != 0) {
+                    store_product_tile_shared<HD, DWL, BIAS>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, fr, bias);
+                } else {
+                    const __nv_bfloat16* xb = grp == 0 ? q + ci.b * p.q.b + h * p.q.h : d_o + ci.b * p.d_o.b + h * p.d_o.h;
+                    const __nv_bfloat16* yb = grp == 0 ? k2 + ci.b * p.k2.b + ci.hk * p.k2.h : v2 + ci.b * p.v2.b + ci.hk * p.v2.h;
+                    form_product_tile<HD, kColTileRows, 128, BIAS>(tile, L::kSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2, xb,
+                                                                   grp == 0 ? p.q.n : p.d_o.n, yb, grp == 0 ? p.k2.n : p.v2.n, bias);
                 }
-                switch (P.dw_log2) {     // whole queries per tile: share the K2 / V2 rows between them
-                    case 4: form_product_tile_shared<HD, 4, BIAS>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
-                    case 5: form_product_tile_shared<HD, 5, BIAS>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
-                    case 6: form_product_tile_shared<HD, 6, BIAS>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, xb, xs, yb, ys, bias); break;
-                    default:
-                        form_product_tile<HD, kColTileRows, 128, BIAS>(tile, L::kSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2, xb, xs,
-                                                                 yb, ys, bias);
-                }
-                if (has_meta) {
+                if (meta_thread) {
                     float* m_lse = (float*)(smem + L::kMeta) + stage * 256;
                     m_lse[row] = meta_lse;
                     m_lse[128 + row] = meta_delta;
                 }
                 fence_proxy_async_smem();
-                mbar_arrive(&st_full[stage]);
+                warp_arrive(&st_full[stage]);
                 if ((warp & 3) == 0) SA_TR(3 + grp, 51);
                 SA_PROF_ADD(37 + grp, t_cform);
-            };
-            for (int t = 0; t < nt; ++t) form_tile(t);
+                // the next tile's rows start travelling now (past the item's end: this tile's once more, never used, so
+                // that the registers are defined on every path)
+                {
+                    const int tn = t + 1 < nt ? t + 1 : t;
+                    SA_COL_LOAD(ci, tn);
+                }
+            }
             g_base += nt;
+        }
+#undef SA_COL_LOAD
+        };      // producer_body
+        switch (P.dw_log2) {
+            case 4: producer_body(std::integral_constant<int, 4>{}); break;
+            case 5: producer_body(std::integral_constant<int, 5>{}); break;
+            case 6: producer_body(std::integral_constant<int, 6>{}); break;
+            default: producer_body(std::integral_constant<int, 0>{});
         }
     } else if (warp == 16) {
         // ---------------------------------------------------------------- MMA issuer
