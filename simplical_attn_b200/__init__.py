@@ -9,6 +9,8 @@ from .simplicial_attn import (TwoSimplicialAttention, TwoSimplicialAttentionFunc
                               two_simplicial_attention, two_simplicial_attn_bwd, two_simplicial_attn_bwd_kv1_kernel,
                               two_simplicial_attn_bwd_kv2_kernel, two_simplicial_attn_fwd_kernel)
 
+from .projection import TwoSimplicialSelfAttention
+
 _REFERENCE_ONLY = ("two_simplicial_attention_reference", "TwoSimplicialAttentionReference")
 
 
@@ -32,4 +34,5 @@ __all__ = [
     "two_simplicial_attn_bwd_kv2_kernel",
     "compute_D_kernel",
     "check_device_status",
+    "TwoSimplicialSelfAttention",
 ]

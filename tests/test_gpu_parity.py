@@ -345,3 +345,27 @@ def test_host_pipeline_matches_device_call(shape):
             assert so.rel_l2(a.float(), b.float().cpu()) <= 2e-3, name
         else:
             assert torch.equal(a, b.cpu()), name
+
+
+def test_projection_module_matches_oracle_and_trains():
+    """Hidden states -> fused input projection -> attention -> output projection: the attention inside reads the
+    five strided views of the projection GEMM's output directly; its result equals the CPU oracle on the same
+    projected tensors, and gradients reach the projection weights."""
+    torch.manual_seed(3)
+    B, N, hidden, H, Hkv, D, w1, w2 = 2, 192, 256, 4, 2, 64, 48, 16
+    mod = sab.TwoSimplicialSelfAttention(hidden, H, D, w1, w2, kv_heads=Hkv, device=DEV)
+    x = (0.5 * torch.randn(B, N, hidden, device=DEV)).to(torch.bfloat16).requires_grad_(True)
+    y = mod(x)
+    assert y.shape == (B, N, hidden) and bool(torch.isfinite(y.float()).all())
+    with torch.no_grad():
+        fused = mod.in_proj(x)
+        parts = [t.float().cpu() for t in torch.split(fused, mod.widths, dim=-1)]
+        q = parts[0].view(B, N, H, D)
+        k1, k2, v1, v2 = (t.view(B, N, Hkv, D) for t in parts[1:])
+        o_ref, _ = so.forward(q, k1, k2, v1, v2, w1, w2, mod.scale)
+        y_ref = torch.nn.functional.linear(o_ref.reshape(B, N, H * D).to(torch.bfloat16).to(DEV), mod.out_proj.weight)
+    assert float((y.float() - y_ref.float()).abs().max()) <= 3e-2
+    y.float().pow(2).mean().backward()
+    for prm in (mod.in_proj.weight, mod.out_proj.weight):
+        assert prm.grad is not None and bool(torch.isfinite(prm.grad.float()).all()) and float(prm.grad.float().abs().sum()) > 0
+    assert x.grad is not None and x.grad.shape == x.shape
