@@ -41,7 +41,7 @@ typedef enum {
 
 typedef enum { SA_BF16 = 0, SA_F16 = 1, SA_F32 = 2 } sa_dtype;
 
-/* Kernel family.  AUTO picks the tcgen05 kernels whenever they cover the problem (bf16, D in
+/* Kernel family.  AUTO picks the tcgen05 kernels whenever they cover the problem (bf16 or fp16, D in
  * {64,128}, effective w2 <= 128) and the general kernels otherwise.  The general kernels are plain
  * CUDA-core fp32 code for every dtype, head dim and window; they also serve as the on-device
  * cross-check of the tensor-core kernels. */

@@ -59,7 +59,7 @@ KParams make_kparams(const sa_params* p) {
 // checked at the call).
 bool tc_shape_ok(const sa_params* p, bool backward) {
     const KParams k = make_kparams(p);
-    if (p->dtype != SA_BF16) return false;
+    if (p->dtype != SA_BF16 && p->dtype != SA_F16) return false;
     if (p->D != 64 && p->D != 128) return false;
     if (k.w2 > 128) return false;
     if (p->scale <= 0.f) return false;            // the row maximum is taken before scaling
@@ -92,9 +92,10 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode() {
     return fn;
 }
 
-// Tensor map over a bf16 [B, rows, heads, D] tensor with (b, n, h) element strides; a box is 64
-// elements of one row by `box_rows` rows, landing 128-byte swizzled.
-bool make_map(CUtensorMap* map, const void* base, int B, int rows, int heads, int D, const sa_strides& st, int box_rows) {
+// Tensor map over a bf16 (or, with `f16`, IEEE half) [B, rows, heads, D] tensor with (b, n, h) element strides;
+// a box is 64 elements of one row by `box_rows` rows, landing 128-byte swizzled.
+bool make_map(CUtensorMap* map, const void* base, int B, int rows, int heads, int D, const sa_strides& st, int box_rows,
+              bool f16) {
     auto enc = get_encode();
     if (!enc) return false;
     cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)heads, (cuuint64_t)B};
@@ -103,7 +104,7 @@ bool make_map(CUtensorMap* map, const void* base, int B, int rows, int heads, in
     cuuint64_t strides[3] = {sb(st.n, rows), sb(st.h, heads), sb(st.b, B)};
     cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+    CUresult r = enc(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
@@ -174,13 +175,14 @@ bool set_smem(Kern kern, int bytes) {
     return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
 }
 
-int launch_fwd_tc(const sa_params* p, const KParams& k, const void* q, const void* k1, const void* k2, const void* v1,
-                  const void* v2, void* o, float* lse, void* workspace, cudaStream_t st) {
+template <bool F16>
+int launch_fwd_tc_t(const KParams& k, const void* q, const void* k1, const void* k2, const void* v1, const void* v2, void* o,
+                    float* lse, void* workspace, cudaStream_t st) {
     DeviceInfo& dev = device_info();
     if (dev.cc_major != 10) return SA_ERR_NOT_SM100;
     CUtensorMap map_k1, map_v1;
-    if (!make_map(&map_k1, k1, k.B, k.n1, k.Hkv, k.D, k.k1, sa::tc::kSubTile)) return SA_ERR_BAD_STRIDE;
-    if (!make_map(&map_v1, v1, k.B, k.n1, k.Hkv, k.D, k.v1, sa::tc::kSubTile)) return SA_ERR_BAD_STRIDE;
+    if (!make_map(&map_k1, k1, k.B, k.n1, k.Hkv, k.D, k.k1, sa::tc::kSubTile, F16)) return SA_ERR_BAD_STRIDE;
+    if (!make_map(&map_v1, v1, k.B, k.n1, k.Hkv, k.D, k.v1, sa::tc::kSubTile, F16)) return SA_ERR_BAD_STRIDE;
     sa::tc::FwdTcParams P{};
     P.k = k;
     P.dw_log2 = dw_log2_of(k.w2);
@@ -190,26 +192,30 @@ int launch_fwd_tc(const sa_params* p, const KParams& k, const void* q, const voi
     P.status = reinterpret_cast<sa::DeviceStatus*>(workspace);
     P.wait_limit_ns = g_wait_limit_ns.load();
     const long grid = P.num_units < dev.sm_count ? P.num_units : dev.sm_count;
-    if (k.D == 128) {
-        using L = sa::tc::FwdSmem<128>;
-        const bool has_bias = k.k2_bias != 0.f || k.v2_bias != 0.f;
-        auto kern = has_bias ? sa::tc::fwd_tc_kernel<128, true> : sa::tc::fwd_tc_kernel<128, false>;
-        if (!set_smem(kern, L::kAlloc)) return SA_ERR_LAUNCH;
-        kern<<<(unsigned)grid, sa::tc::kFwdThreads, L::kAlloc, st>>>(P, map_k1, map_v1, (const __nv_bfloat16*)q,
-                                                                      (const __nv_bfloat16*)k2, (const __nv_bfloat16*)v2,
-                                                                      (__nv_bfloat16*)o, lse);
-    } else {
-        using L = sa::tc::FwdSmem<64>;
-        const bool has_bias = k.k2_bias != 0.f || k.v2_bias != 0.f;
-        auto kern = has_bias ? sa::tc::fwd_tc_kernel<64, true> : sa::tc::fwd_tc_kernel<64, false>;
-        if (!set_smem(kern, L::kAlloc)) return SA_ERR_LAUNCH;
-        kern<<<(unsigned)grid, sa::tc::kFwdThreads, L::kAlloc, st>>>(P, map_k1, map_v1, (const __nv_bfloat16*)q,
-                                                                      (const __nv_bfloat16*)k2, (const __nv_bfloat16*)v2,
-                                                                      (__nv_bfloat16*)o, lse);
-    }
-    (void)p;
+    const bool has_bias = k.k2_bias != 0.f || k.v2_bias != 0.f;
+    auto launch = [&](auto kern, int smem_bytes) {
+        if (!set_smem(kern, smem_bytes)) return false;
+        kern<<<(unsigned)grid, sa::tc::kFwdThreads, smem_bytes, st>>>(P, map_k1, map_v1, (const __nv_bfloat16*)q,
+                                                                       (const __nv_bfloat16*)k2, (const __nv_bfloat16*)v2,
+                                                                       (__nv_bfloat16*)o, lse);
+        return true;
+    };
+    bool ok;
+    if (k.D == 128)
+        ok = has_bias ? launch(sa::tc::fwd_tc_kernel<128, true, F16>, sa::tc::FwdSmem<128>::kAlloc)
+                      : launch(sa::tc::fwd_tc_kernel<128, false, F16>, sa::tc::FwdSmem<128>::kAlloc);
+    else
+        ok = has_bias ? launch(sa::tc::fwd_tc_kernel<64, true, F16>, sa::tc::FwdSmem<64>::kAlloc)
+                      : launch(sa::tc::fwd_tc_kernel<64, false, F16>, sa::tc::FwdSmem<64>::kAlloc);
+    if (!ok) return SA_ERR_LAUNCH;
     g_launches += 1;
     return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
+}
+
+int launch_fwd_tc(const sa_params* p, const KParams& k, const void* q, const void* k1, const void* k2, const void* v1,
+                  const void* v2, void* o, float* lse, void* workspace, cudaStream_t st) {
+    return p->dtype == SA_F16 ? launch_fwd_tc_t<true>(k, q, k1, k2, v1, v2, o, lse, workspace, st)
+                              : launch_fwd_tc_t<false>(k, q, k1, k2, v1, v2, o, lse, workspace, st);
 }
 
 int resolve(const sa_params* p, bool backward) {
@@ -363,7 +369,7 @@ int sa_backward(const sa_params* p, const void* q, const void* k1, const void* k
         const int rc = sa::tc::launch_bwd(k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2,
                                           static_cast<uint8_t*>(workspace) + kStatusBytes,
                                           reinterpret_cast<sa::DeviceStatus*>(workspace), st, &nlaunch, &make_map,
-                                          plan_sm_count(), g_wait_limit_ns.load());
+                                          plan_sm_count(), g_wait_limit_ns.load(), p->dtype == SA_F16);
         g_launches += nlaunch;
         if (rc != -1) return rc;      // -1: the tensor-core backward declines this problem
         if (p->algo == SA_ALGO_TCGEN05) return SA_ERR_UNSUPPORTED;

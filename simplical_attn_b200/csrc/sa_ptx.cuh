@@ -4,6 +4,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -294,8 +295,10 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t slab_by
 
 // Instruction descriptor: D fp32 (bits 4-5 = 1), A and B bf16 (bits 7-9, 10-12 = 1), optional
 // MN-major A (bit 15) / B (bit 16), N >> 3 at bit 17, M >> 4 at bit 24.
-__host__ __device__ __forceinline__ uint32_t make_idesc(int m, int n, bool a_mn_major, bool b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+// `f16`: both operands are IEEE half (format 0) instead of bf16 (format 1).
+__host__ __device__ __forceinline__ uint32_t make_idesc(int m, int n, bool a_mn_major, bool b_mn_major, bool f16 = false) {
+    const uint32_t fmt = f16 ? 0u : 1u;
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
@@ -356,6 +359,54 @@ __device__ __forceinline__ float ex2(float x) {
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
+// The 16-bit element type of the tensor-core kernels: bf16 (F16 = false) or IEEE half (F16 = true).  The
+// kernels move elements as raw 16-bit patterns (pointers are typed __nv_bfloat16 for their size only);
+// everything that depends on the encoding goes through this struct.
+template <bool F16>
+struct El {
+    // two floats -> one packed word (lo in the low half)
+    static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+        uint32_t r;
+        if constexpr (F16) asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+        else asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+        return r;
+    }
+    static __device__ __forceinline__ float lo(uint32_t w) {
+        if constexpr (F16) {
+            float f;
+            asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %1;\n\tcvt.f32.f16 %0, l;\n\t}" : "=f"(f) : "r"(w));
+            return f;
+        } else {
+            return __uint_as_float(w << 16);
+        }
+    }
+    static __device__ __forceinline__ float hi(uint32_t w) {
+        if constexpr (F16) {
+            float f;
+            asm("{\n\t.reg .b16 l, h;\n\tmov.b32 {l, h}, %1;\n\tcvt.f32.f16 %0, h;\n\t}" : "=f"(f) : "r"(w));
+            return f;
+        } else {
+            return __uint_as_float(w & 0xffff0000u);
+        }
+    }
+    // one element to / from its 16-bit slot
+    static __device__ __forceinline__ void st(__nv_bfloat16* p, float v) {
+        if constexpr (F16) *reinterpret_cast<__half*>(p) = __float2half_rn(v);
+        else *p = __float2bfloat16_rn(v);
+    }
+    static __device__ __forceinline__ float2 ld2(const __nv_bfloat16* p) {      // two consecutive elements (4-byte aligned)
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+        return make_float2(lo(w), hi(w));
+    }
+    // elementwise product of two packed pairs, rounded once (exact: the product of two such significands fits fp32)
+    static __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+        uint32_t r;
+        if constexpr (F16) asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        else asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+        return r;
+    }
+};
+
 // Loads N consecutive bf16 values (N a multiple of 8, 16-byte aligned) as N/2 packed words.
 template <int N>
 __device__ __forceinline__ void load_bf16_words(const __nv_bfloat16* src, uint32_t (&w)[N / 2]) {
@@ -369,13 +420,15 @@ __device__ __forceinline__ void load_bf16_words(const __nv_bfloat16* src, uint32
     }
 }
 
-// Product of two bf16 chunks of 8 elements, x * (y + bias), computed in fp32 and rounded once.
+// Product of two chunks of 8 elements, x * (y + bias), computed in fp32 and rounded once.
+template <bool F16 = false>
 __device__ __forceinline__ uint4 mul_chunk(const uint4& xa, const uint4& ya, float bias) {
+    using E = El<F16>;
     const uint32_t xw[4] = {xa.x, xa.y, xa.z, xa.w}, yw[4] = {ya.x, ya.y, ya.z, ya.w};
     uint32_t w[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e)
-        w[e] = pack_bf16(bf16_lo(xw[e]) * (bf16_lo(yw[e]) + bias), bf16_hi(xw[e]) * (bf16_hi(yw[e]) + bias));
+        w[e] = E::pack(E::lo(xw[e]) * (E::lo(yw[e]) + bias), E::hi(xw[e]) * (E::hi(yw[e]) + bias));
     return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
@@ -386,12 +439,14 @@ __device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
     asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
     return r;
 }
+template <bool F16 = false>
 __device__ __forceinline__ uint4 mul_chunk_nobias(const uint4& xa, const uint4& ya) {
-    return make_uint4(hmul2_bf16(xa.x, ya.x), hmul2_bf16(xa.y, ya.y), hmul2_bf16(xa.z, ya.z), hmul2_bf16(xa.w, ya.w));
+    using E = El<F16>;
+    return make_uint4(E::mul2(xa.x, ya.x), E::mul2(xa.y, ya.y), E::mul2(xa.z, ya.z), E::mul2(xa.w, ya.w));
 }
 
 // BIAS = false: the bias is known to be zero (the common case) and the exact packed-bf16 product is used.
-template <int HD, int NROWS, int NTHREADS, bool BIAS, int MAXBATCH = 4>
+template <int HD, int NROWS, int NTHREADS, bool BIAS, bool F16 = false, int MAXBATCH = 4>
 __device__ __forceinline__ void form_product_tile(uint8_t* tile, int slab_bytes, int t, long rho0, int dw_log2, int n_q,
                                                   int w2, int halo2, const __nv_bfloat16* x, int64_t xs,
                                                   const __nv_bfloat16* y, int64_t ys, float bias) {
@@ -423,7 +478,7 @@ __device__ __forceinline__ void form_product_tile(uint8_t* tile, int slab_bytes,
         for (int k = 0; k < BATCH; ++k) {
             const int r = t / C + (k0 + k) * RPP;
             uint4 out = make_uint4(0, 0, 0, 0);
-            if (ok[k]) out = BIAS ? mul_chunk(xa[k], ya[k], bias) : mul_chunk_nobias(xa[k], ya[k]);
+            if (ok[k]) out = BIAS ? mul_chunk<F16>(xa[k], ya[k], bias) : mul_chunk_nobias<F16>(xa[k], ya[k]);
             *(uint4*)(tile + (c >> 3) * slab_bytes + r * 128 + (((c & 7) ^ (r & 7)) << 4)) = out;
         }
     }
@@ -469,7 +524,7 @@ __device__ __forceinline__ void load_product_tile_shared(uint4* regs, int t, int
     }
 }
 
-template <int HD, int DWLOG, bool BIAS, int NTHREADS = 128>
+template <int HD, int DWLOG, bool BIAS, bool F16 = false, int NTHREADS = 128>
 __device__ __forceinline__ void store_product_tile_shared(uint8_t* tile, int slab_bytes, int t, int i0, int n_q, int w2, int halo2,
                                                           const uint4* regs, float bias) {
     using S = ProductTileShape<HD, DWLOG, NTHREADS>;
@@ -495,13 +550,13 @@ __device__ __forceinline__ void store_product_tile_shared(uint8_t* tile, int sla
             bool ok = dlt < lim;
             if (BIAS) ok = ok && q_ok && (kb_first + pr + k * RPP >= 0);
             uint4 out = make_uint4(0, 0, 0, 0);
-            if (ok) out = BIAS ? mul_chunk(regs[q2], regs[NQ + k], bias) : mul_chunk_nobias(regs[q2], regs[NQ + k]);
+            if (ok) out = BIAS ? mul_chunk<F16>(regs[q2], regs[NQ + k], bias) : mul_chunk_nobias<F16>(regs[q2], regs[NQ + k]);
             *(uint4*)(bq - 128 * RPP * k) = out;
         }
     }
 }
 
-template <int HD, int DWLOG, bool BIAS, int NTHREADS = 128>
+template <int HD, int DWLOG, bool BIAS, bool F16 = false, int NTHREADS = 128>
 __device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab_bytes, int t, int i0, int n_q, int w2,
                                                          int halo2, const __nv_bfloat16* x, int64_t xs,
                                                          const __nv_bfloat16* y, int64_t ys, float bias) {
@@ -514,7 +569,7 @@ __device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab
     SA_PROF_ADD(60, t_ld);
     SA_PROF_T0(t_st);
 #endif
-    store_product_tile_shared<HD, DWLOG, BIAS, NTHREADS>(tile, slab_bytes, t, i0, n_q, w2, halo2, regs, bias);
+    store_product_tile_shared<HD, DWLOG, BIAS, F16, NTHREADS>(tile, slab_bytes, t, i0, n_q, w2, halo2, regs, bias);
 #ifdef SA_PROFILE
     SA_PROF_ADD(61, t_st);
 #endif
@@ -522,16 +577,16 @@ __device__ __forceinline__ void form_product_tile_shared(uint8_t* tile, int slab
 
 // A 128-row product tile that starts at query i0 (DW = 1 << dw_log2 delta slots per query): the
 // shared-window form for 16, 32 and 64 slots (one round of loads), the general form otherwise.
-template <int HD, bool BIAS>
+template <int HD, bool BIAS, bool F16 = false>
 __device__ __forceinline__ void form_query_tile(uint8_t* tile, int slab_bytes, int t, int i0, int dw_log2, int n_q, int w2,
                                                 int halo2, const __nv_bfloat16* x, int64_t xs, const __nv_bfloat16* y,
                                                 int64_t ys, float bias) {
     switch (dw_log2) {
-        case 4: form_product_tile_shared<HD, 4, BIAS>(tile, slab_bytes, t, i0, n_q, w2, halo2, x, xs, y, ys, bias); break;
-        case 5: form_product_tile_shared<HD, 5, BIAS>(tile, slab_bytes, t, i0, n_q, w2, halo2, x, xs, y, ys, bias); break;
-        case 6: form_product_tile_shared<HD, 6, BIAS>(tile, slab_bytes, t, i0, n_q, w2, halo2, x, xs, y, ys, bias); break;
+        case 4: form_product_tile_shared<HD, 4, BIAS, F16>(tile, slab_bytes, t, i0, n_q, w2, halo2, x, xs, y, ys, bias); break;
+        case 5: form_product_tile_shared<HD, 5, BIAS, F16>(tile, slab_bytes, t, i0, n_q, w2, halo2, x, xs, y, ys, bias); break;
+        case 6: form_product_tile_shared<HD, 6, BIAS, F16>(tile, slab_bytes, t, i0, n_q, w2, halo2, x, xs, y, ys, bias); break;
         default:
-            form_product_tile<HD, 128, 128, BIAS>(tile, slab_bytes, t, (long)i0 << dw_log2, dw_log2, n_q, w2, halo2, x, xs, y, ys, bias);
+            form_product_tile<HD, 128, 128, BIAS, F16>(tile, slab_bytes, t, (long)i0 << dw_log2, dw_log2, n_q, w2, halo2, x, xs, y, ys, bias);
     }
 }
 

@@ -90,6 +90,7 @@ struct BwdSmem {
 // ------------------------------------------------------------------------------------------------
 // 1. Delta and LSE2
 // ------------------------------------------------------------------------------------------------
+template <bool F16>
 __global__ void __launch_bounds__(128)
 prep_kernel(KParams p, const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
             const float* __restrict__ lse, float* __restrict__ lse2, float* __restrict__ delta) {
@@ -103,8 +104,8 @@ prep_kernel(KParams p, const __nv_bfloat16* __restrict__ o, const __nv_bfloat16*
     const __nv_bfloat16* drow = d_o + b * p.d_o.b + (long)i * p.d_o.n + h * p.d_o.h;
     float s = 0.f;
     for (int d = lane * 2; d < p.D; d += 64) {
-        const float2 a = __bfloat1622float2(*(const __nv_bfloat162*)(orow + d));
-        const float2 c = __bfloat1622float2(*(const __nv_bfloat162*)(drow + d));
+        const float2 a = ptx::El<F16>::ld2(orow + d);
+        const float2 c = ptx::El<F16>::ld2(drow + d);
         s = fmaf(a.x, c.x, s);
         s = fmaf(a.y, c.y, s);
     }
@@ -117,7 +118,7 @@ prep_kernel(KParams p, const __nv_bfloat16* __restrict__ o, const __nv_bfloat16*
 
 // P = mask ? exp2(s*c2 - lse2) : 0 and dS = P * (dp - delta) for W columns, packed to bf16.
 // MASKED selects per-column validity through lo/hi (tile-relative valid column range).
-template <bool MASKED, int W = 32>
+template <bool MASKED, int W = 32, bool F16 = false>
 __device__ __forceinline__ void softmax_bwd_chunk(const uint32_t (&s)[W], const uint32_t (&dp)[W], int c0, int lo, int hi,
                                                   float c2, float lse2, float delta, uint32_t (&pp)[W / 2], uint32_t (&ds)[W / 2]) {
     // packed two-wide fp32 arithmetic (one instruction per pair of columns)
@@ -137,8 +138,8 @@ __device__ __forceinline__ void softmax_bwd_chunk(const uint32_t (&s)[W], const 
             d.x = (c >= lo && c <= hi) ? d.x : 0.f;
             d.y = (c + 1 >= lo && c + 1 <= hi) ? d.y : 0.f;
         }
-        pp[e >> 1] = ptx::pack_bf16(pr.x, pr.y);
-        ds[e >> 1] = ptx::pack_bf16(d.x, d.y);
+        pp[e >> 1] = ptx::El<F16>::pack(pr.x, pr.y);
+        ds[e >> 1] = ptx::El<F16>::pack(d.x, d.y);
     }
 }
 
@@ -216,11 +217,11 @@ __device__ __forceinline__ void issue_sdp(uint32_t leader, uint32_t tm_s, uint32
 
 // SPLIT: P and dS of a tile were written by two groups, each into the first 16 columns of its own 32-column half
 // of the buffer (k-steps 0, 1 at columns 0..15, k-steps 2, 3 at columns 32..47); otherwise packed at columns 0..31.
-template <int HD, bool SPLIT = false>
+template <int HD, bool SPLIT = false, bool F16 = false>
 __device__ __forceinline__ void issue_acc(uint32_t leader, uint32_t tm_acc1, uint32_t tm_acc2, uint32_t tm_p, uint32_t tm_ds, uint32_t w,
                                           uint32_t z, int ksteps, bool accumulate) {
     using L = BwdSmem<HD>;
-    const uint32_t idesc = ptx::make_idesc(128, HD, false, true);
+    const uint32_t idesc = ptx::make_idesc(128, HD, false, true, F16);
     const uint64_t dw = ptx::desc_mnmajor(w, L::kSmallSlab), dz = ptx::desc_mnmajor(z, L::kSmallSlab);
     auto col = [](int kk) { return SPLIT ? (kk >> 1) * 32 + (kk & 1) * 8 : kk * 8; };
     if (ksteps == kStreamRows / 16) {
@@ -261,7 +262,7 @@ struct ColSmem {
 // shared memory either way) and in long bursts.  S^T / dP^T are not double buffered (tensor memory
 // is full: 128 + 128 + 2 x 128 accumulator columns); instead both softmax groups work on the same
 // tile, group g on columns [64g, 64g + 64), and write P / dS back inside their own column range.
-template <int HD, bool BIAS>
+template <int HD, bool BIAS, bool F16 = false>
 __global__ void __launch_bounds__(kColThreads, 1)
 bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
                const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
@@ -269,6 +270,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dk1, __nv_bfloat16* __restrict__ dv1) {
     using L = ColSmem<HD>;
     using namespace ptx;
+    using E = El<F16>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
@@ -363,7 +365,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             const int i = (int)((rho0 + c0) >> P.dw_log2);
                             const bool valid = !MASKED || ((jb <= i + p.halo1) && (jb >= i + p.halo1 - p.w1 + 1));
                             uint32_t pp[8], ds[8];
-                            softmax_bwd_chunk<MASKED, 16>(s[k & 1], dp[k & 1], 0, valid ? 0 : 1, valid ? 15 : 0, c2, m_lse[i - iq0],
+                            softmax_bwd_chunk<MASKED, 16, F16>(s[k & 1], dp[k & 1], 0, valid ? 0 : 1, valid ? 15 : 0, c2, m_lse[i - iq0],
                                                           m_delta[i - iq0], pp, ds);
                             // packed P^T / dS^T of columns [64g + 16k, +16) go to tensor-memory columns 64g + 8k ...
                             tmem_st8(tm_s + lane_addr + 64 * grp + 8 * k, pp);
@@ -395,8 +397,8 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                                 pv[x] = valid ? pe : 0.f;
                                 dv[x] = valid ? pe * (__uint_as_float(dp[e + x]) - m_delta[i - iq0]) : 0.f;
                             }
-                            pp[e >> 1] = pack_bf16(pv[0], pv[1]);
-                            ds[e >> 1] = pack_bf16(dv[0], dv[1]);
+                            pp[e >> 1] = E::pack(pv[0], pv[1]);
+                            ds[e >> 1] = E::pack(dv[0], dv[1]);
                         }
                         tmem_st8(tm_s + lane_addr + 64 * grp + (cc >> 1), pp);
                         tmem_st8(tm_dp + lane_addr + 64 * grp + (cc >> 1), ds);
@@ -433,10 +435,10 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                     uint4* dst = (uint4*)(out + ci.b * st.b + (long)jb * st.n + ci.hk * st.h + c0);
 #pragma unroll
                     for (int x = 0; x < 4; ++x)
-                        dst[x] = make_uint4(pack_bf16(__uint_as_float(v[8 * x]) * mult, __uint_as_float(v[8 * x + 1]) * mult),
-                                            pack_bf16(__uint_as_float(v[8 * x + 2]) * mult, __uint_as_float(v[8 * x + 3]) * mult),
-                                            pack_bf16(__uint_as_float(v[8 * x + 4]) * mult, __uint_as_float(v[8 * x + 5]) * mult),
-                                            pack_bf16(__uint_as_float(v[8 * x + 6]) * mult, __uint_as_float(v[8 * x + 7]) * mult));
+                        dst[x] = make_uint4(E::pack(__uint_as_float(v[8 * x]) * mult, __uint_as_float(v[8 * x + 1]) * mult),
+                                            E::pack(__uint_as_float(v[8 * x + 2]) * mult, __uint_as_float(v[8 * x + 3]) * mult),
+                                            E::pack(__uint_as_float(v[8 * x + 4]) * mult, __uint_as_float(v[8 * x + 5]) * mult),
+                                            E::pack(__uint_as_float(v[8 * x + 6]) * mult, __uint_as_float(v[8 * x + 7]) * mult));
                 }
             }
             if (nt > 0) {
@@ -496,11 +498,11 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const float bias = BIAS ? (grp == 0 ? p.k2_bias : p.v2_bias) : 0.f;
                 const int iq0 = (int)(rho0 >> P.dw_log2);
                 if constexpr (DWL != 0) {
-                    store_product_tile_shared<HD, DWL, BIAS>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, fr, bias);
+                    store_product_tile_shared<HD, DWL, BIAS, F16>(tile, L::kSlab, row, iq0, p.N, p.w2, p.halo2, fr, bias);
                 } else {
                     const __nv_bfloat16* xb = grp == 0 ? q + ci.b * p.q.b + h * p.q.h : d_o + ci.b * p.d_o.b + h * p.d_o.h;
                     const __nv_bfloat16* yb = grp == 0 ? k2 + ci.b * p.k2.b + ci.hk * p.k2.h : v2 + ci.b * p.v2.b + ci.hk * p.v2.h;
-                    form_product_tile<HD, kColTileRows, 128, BIAS>(tile, L::kSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2, xb,
+                    form_product_tile<HD, kColTileRows, 128, BIAS, F16>(tile, L::kSlab, row, rho0, P.dw_log2, p.N, p.w2, p.halo2, xb,
                                                                    grp == 0 ? p.q.n : p.d_o.n, yb, grp == 0 ? p.k2.n : p.v2.n, bias);
                 }
                 if (meta_thread) {
@@ -535,8 +537,8 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         {
             const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
             uint32_t g_base = 0, n_items = 0;
-            const uint32_t idesc_sd = make_idesc(128, kColTileRows, false, false);
-            const uint32_t idesc_acc = make_idesc(128, HD, false, true);
+            const uint32_t idesc_sd = make_idesc(128, kColTileRows, false, false, F16);
+            const uint32_t idesc_acc = make_idesc(128, HD, false, true, F16);
             const uint64_t d_k1 = desc_kmajor(smem_base + L::kK1, 0), d_v1 = desc_kmajor(smem_base + L::kV1, 0);
             for (long it = blockIdx.x; it < P.num_col_items; it += gridDim.x) {
                 const ColItem ci = col_item(P, it);
@@ -682,22 +684,6 @@ __device__ __forceinline__ void tmem_ld_cw(uint32_t addr, uint32_t (&v)[CW]) {
     ptx::tmem_wait_ld();
 }
 
-// CW bf16 values of a row starting at element `col`, plus `bias`, as floats.
-template <int CW>
-__device__ __forceinline__ void load_bf16_cw(const __nv_bfloat16* row, int col, float bias, float (&out)[CW]) {
-#pragma unroll
-    for (int x = 0; x < CW / 8; ++x) {
-        const uint4 raw = ((const uint4*)(row + col))[x];
-        const __nv_bfloat162* h2 = (const __nv_bfloat162*)&raw;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(h2[e]);
-            out[8 * x + 2 * e] = f.x + bias;
-            out[8 * x + 2 * e + 1] = f.y + bias;
-        }
-    }
-}
-
 
 // Index into a ring of fp32 rows [slot][HD + 2]: with this row pitch the same column pair of 32
 // consecutive rows falls into different banks for 8-byte accesses, a column offset known at compile
@@ -707,7 +693,7 @@ __device__ __forceinline__ int ring_index(int slot, int col) {
     return slot * (HD + 2) + col;
 }
 
-template <int HD, int NS, bool TWOQ, bool BIAS>
+template <int HD, int NS, bool TWOQ, bool BIAS, bool F16 = false>
 __global__ void __launch_bounds__(kRowThreads, 1)
 bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
                const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
@@ -715,6 +701,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dq, int need_kv2, int ring_rows) {
     using L = BwdSmem<HD, NS>;
     using namespace ptx;
+    using E = El<F16>;
     constexpr int CW = HD / 4;                            // epilogue chunk width
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -792,11 +779,11 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 // ---- stationary operand of this group
                 SA_PROF_T0(t_form);
                 if (grp == 0)
-                    form_query_tile<HD, BIAS>(my_tile, L::kBigSlab, row, i0, P.dw_log2, p.N, p.w2, p.halo2,
+                    form_query_tile<HD, BIAS, F16>(my_tile, L::kBigSlab, row, i0, P.dw_log2, p.N, p.w2, p.halo2,
                                               q + ri.b * p.q.b + ri.h * p.q.h, p.q.n, k2 + ri.b * p.k2.b + ri.hk * p.k2.h, p.k2.n,
                                               BIAS ? p.k2_bias : 0.f);
                 else
-                    form_query_tile<HD, BIAS>(my_tile, L::kBigSlab, row, i0, P.dw_log2, p.N, p.w2, p.halo2,
+                    form_query_tile<HD, BIAS, F16>(my_tile, L::kBigSlab, row, i0, P.dw_log2, p.N, p.w2, p.halo2,
                                               d_o + ri.b * p.d_o.b + ri.h * p.d_o.h, p.d_o.n,
                                               v2 + ri.b * p.v2.b + ri.hk * p.v2.h, p.v2.n, BIAS ? p.v2_bias : 0.f);
                 fence_proxy_async_smem();
@@ -823,8 +810,8 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         tmem_ld32(tm_s[grp] + lane_addr + c0, s);
                         tmem_ld32(tm_dp[grp] + lane_addr + c0, dp);
                         tmem_wait_ld();
-                        if (full) softmax_bwd_chunk<false>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
-                        else softmax_bwd_chunk<true>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
+                        if (full) softmax_bwd_chunk<false, 32, F16>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
+                        else softmax_bwd_chunk<true, 32, F16>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
                         tmem_st16(tm_s[grp] + lane_addr + (c0 >> 1), pp);
                         tmem_st16(tm_dp[grp] + lane_addr + (c0 >> 1), ds);
                     }
@@ -880,22 +867,22 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 #pragma unroll
                                 for (int e = 0; e < CW; e += 2) {
                                     const float2 t = __fmul2_rn(make_float2(__uint_as_float(g[e]), __uint_as_float(g[e + 1])),
-                                                                make_float2(bf16_lo(xw[e >> 1]), bf16_hi(xw[e >> 1])));
+                                                                make_float2(E::lo(xw[e >> 1]), E::hi(xw[e >> 1])));
                                     v[e] = t.x;
                                     v[e + 1] = t.y;
                                 }
                             } else {
 #pragma unroll
                                 for (int e = 0; e < CW; e += 2) {
-                                    v[e] = __uint_as_float(g[e]) * (bf16_lo(xw[e >> 1]) + p.k2_bias);
-                                    v[e + 1] = __uint_as_float(g[e + 1]) * (bf16_hi(xw[e >> 1]) + p.k2_bias);
+                                    v[e] = __uint_as_float(g[e]) * (E::lo(xw[e >> 1]) + p.k2_bias);
+                                    v[e + 1] = __uint_as_float(g[e + 1]) * (E::hi(xw[e >> 1]) + p.k2_bias);
                                 }
                             }
                             if constexpr (!two_q) {
                                 const float tot = warp_transpose_reduce<CW>(v, lane) * mult;
                                 if (lane < CW) {
                                     if (ppq == 1) {      // the warp holds the whole query: its dQ columns are final
-                                        if (i0 + wq < p.N) dq_out[(long)wq * p.dq.n + c * CW + lane] = __float2bfloat16_rn(tot);
+                                        if (i0 + wq < p.N) E::st(&dq_out[(long)wq * p.dq.n + c * CW + lane], tot);
                                     } else {
                                         dq_part[part_row * HD + c * CW + lane] = tot;
                                     }
@@ -908,7 +895,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                                     for (int e = 0; e < 16; ++e) vv[e] = v[16 * hb + e];
                                     const float tot = half_warp_transpose_reduce16(vv, lane) * mult;
                                     if (i0 + part_row < p.N)
-                                        dq_out[(long)part_row * p.dq.n + c * CW + 16 * hb + (lane & 15)] = __float2bfloat16_rn(tot);
+                                        E::st(&dq_out[(long)part_row * p.dq.n + c * CW + 16 * hb + (lane & 15)], tot);
                                 }
                             }
                         }
@@ -925,7 +912,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 #pragma unroll
                                 for (int e = 0; e < CW / 2; ++e)
                                     acc_r[e] = __ffma2_rn(make_float2(__uint_as_float(g[2 * e]), __uint_as_float(g[2 * e + 1])),
-                                                          make_float2(bf16_lo(yw[e]), bf16_hi(yw[e])), acc_r[e]);
+                                                          make_float2(E::lo(yw[e]), E::hi(yw[e])), acc_r[e]);
 #pragma unroll
                                 for (int e = 0; e < CW / 2; ++e) rp[e] = acc_r[e];
                             }
@@ -944,7 +931,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                                 float a = 0.f;
                                 for (int w2i = 0; w2i < ppq; ++w2i) a += dq_part[(q2 * ppq + w2i) * HD + row];
                                 if (i0 + q2 < p.N)
-                                    dq[ri.b * p.dq.b + (long)(i0 + q2) * p.dq.n + ri.h * p.dq.h + row] = __float2bfloat16_rn(a);
+                                    E::st(&dq[ri.b * p.dq.b + (long)(i0 + q2) * p.dq.n + ri.h * p.dq.h + row], a);
                             }
                         }
                         named_barrier_sync(1 + grp, 128);
@@ -963,13 +950,13 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                         load_bf16_words<CW>(k2_row + c * CW, xw);
 #pragma unroll
                         for (int e = 0; e < CW; ++e) {
-                            const float xf = ((e & 1) ? bf16_hi(xw[e >> 1]) : bf16_lo(xw[e >> 1])) + (BIAS ? p.k2_bias : 0.f);
+                            const float xf = ((e & 1) ? E::hi(xw[e >> 1]) : E::lo(xw[e >> 1])) + (BIAS ? p.k2_bias : 0.f);
                             scr_a[row * CW + (e ^ (row & (CW - 1)))] = row_valid ? __uint_as_float(g[e]) * xf * mult : 0.f;
                         }
                     }
 #pragma unroll
                     for (int e = 0; e < CW; ++e) {
-                        const float yf = (e & 1) ? bf16_hi(yw[e >> 1]) : bf16_lo(yw[e >> 1]);
+                        const float yf = (e & 1) ? E::hi(yw[e >> 1]) : E::lo(yw[e >> 1]);
                         scr_b[row * CW + (e ^ (row & (CW - 1)))] = row_valid ? __uint_as_float(g[e]) * yf : 0.f;
                     }
                     named_barrier_sync(1 + grp, 128);
@@ -982,7 +969,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                                 a += scr_a[rr * CW + (e ^ (rr & (CW - 1)))];
                             }
                             if (i0 + q2 < p.N)
-                                dq[ri.b * p.dq.b + (long)(i0 + q2) * p.dq.n + ri.h * p.dq.h + c * CW + e] = __float2bfloat16_rn(a);
+                                E::st(&dq[ri.b * p.dq.b + (long)(i0 + q2) * p.dq.n + ri.h * p.dq.h + c * CW + e], a);
                         }
                     }
                     if (need_kv2) {
@@ -1054,7 +1041,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         {
             const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
             uint32_t nb[2] = {0, 0}, g_base = 0, n_units = 0;
-            const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false);
+            const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false, F16);
             const uint32_t a_s = smem_base + L::kStat0, c_s = smem_base + L::kStat1;
             for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
                 const RowItem ri = row_item(P, it);
@@ -1072,7 +1059,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             mbar_wait(&B.st_full[stage], (g / NS) & 1, wctx, 33);
                             tc_fence_after();
                             SA_PROF_T0(t_i1);
-                            issue_sdp<HD>(leader, tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false));
+                            issue_sdp<HD>(leader, tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false, F16));
                             tc_commit(leader, &B.sdp_ready[b]);
                             SA_PROF_ADD(47, t_i1);
                         }
@@ -1087,7 +1074,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                             tc_fence_after();
                             // U += P V1-tile ; G += dS K1-tile
                             SA_PROF_T0(t_i2);
-                            issue_acc<HD>(leader, tm_u, tm_g, tm_s[b], tm_dp[b], k1_t, v1_t, width / 16, tp > 0);
+                            issue_acc<HD, false, F16>(leader, tm_u, tm_g, tm_s[b], tm_dp[b], k1_t, v1_t, width / 16, tp > 0);
                             tc_commit(leader, &B.st_empty[stage]);
                             SA_PROF_ADD(48, t_i2);
                         }
@@ -1155,7 +1142,7 @@ constexpr int row2_stage_bytes(int dwl, int hd) {
 
 constexpr int kRow2Threads = 640;     // softmax groups (0-7), epilogue groups (8-15), MMA issuers (16, 17), TMA (18), 1 idle
 
-template <int HD, int DWL, int NS, bool BIAS>
+template <int HD, int DWL, int NS, bool BIAS, bool F16 = false>
 __global__ void __launch_bounds__(kRow2Threads, 1)
 bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
                 const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
@@ -1163,6 +1150,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                 const __nv_bfloat16* __restrict__ d_o, __nv_bfloat16* __restrict__ dq, int need_kv2, int ring_rows) {
     using L = BwdSmem<HD, NS>;
     using namespace ptx;
+    using E = El<F16>;
     constexpr int CW = 16;                                // epilogue chunk width
     constexpr int NPH = HD / CW;                          // epilogue phases
     static_assert(DWL >= 4 && DWL <= 6, "16, 32 or 64 delta slots per query");
@@ -1268,7 +1256,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
             if (n_units > 0) mbar_wait(B.stat_empty, (n_units - 1) & 1, wctx, 37);
             if ((warp & 3) == 0) SA_TR(1 + grp, 50);
             SA_PROF_T0(t_form);
-            store_product_tile_shared<HD, DWL, BIAS>(my_tile, L::kBigSlab, row, i0, p.N, p.w2, p.halo2, fr, bias);
+            store_product_tile_shared<HD, DWL, BIAS, F16>(my_tile, L::kBigSlab, row, i0, p.N, p.w2, p.halo2, fr, bias);
             if constexpr (STAGE) {
                 using S = ProductTileShape<HD, DWL>;
                 const int sb = n_units & 1;                              // this unit's staging buffer; its (n_units >> 1)-th use
@@ -1316,8 +1304,8 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                     tmem_ld32(tm_s[b] + lane_addr + c0, s);
                     tmem_ld32(tm_dp[b] + lane_addr + c0, dp);
                     tmem_wait_ld();
-                    if (full) softmax_bwd_chunk<false>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
-                    else softmax_bwd_chunk<true>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
+                    if (full) softmax_bwd_chunk<false, 32, F16>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
+                    else softmax_bwd_chunk<true, 32, F16>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
                     tmem_st16(tm_s[b] + lane_addr + c0, pp);
                     tmem_st16(tm_dp[b] + lane_addr + c0, ds);
                     tmem_wait_st();
@@ -1419,7 +1407,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                         float v[CW];
 #pragma unroll
                         for (int e = 0; e < CW; e += 2) {
-                            float2 x2 = make_float2(bf16_lo(xw[e >> 1]), bf16_hi(xw[e >> 1]));
+                            float2 x2 = make_float2(E::lo(xw[e >> 1]), E::hi(xw[e >> 1]));
                             if (BIAS) x2 = __fadd2_rn(x2, make_float2(p.k2_bias, p.k2_bias));
                             const float2 t = __fmul2_rn(make_float2(__uint_as_float(g[e]), __uint_as_float(g[e + 1])), x2);
                             v[e] = t.x;
@@ -1428,7 +1416,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                         if constexpr (!TWO_Q) {
                             const float tot = warp_transpose_reduce<CW>(v, lane) * p.scale;
                             if (WPQ == 1) {
-                                if (lane < CW && i0 + wq < p.N) dq_out[(long)wq * p.dq.n + c + lane] = __float2bfloat16_rn(tot);
+                                if (lane < CW && i0 + wq < p.N) E::st(&dq_out[(long)wq * p.dq.n + c + lane], tot);
                             } else if (lane < CW) {
                                 dq_part[wq * HALF + c + lane] = tot;
                             }
@@ -1436,7 +1424,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                             // each half warp holds the 16 deltas of one query
                             const int qh = wq * 2 + (lane >> 4);
                             const float tot = half_warp_transpose_reduce16(v, lane) * p.scale;
-                            if (i0 + qh < p.N) dq_out[(long)qh * p.dq.n + c + (lane & 15)] = __float2bfloat16_rn(tot);
+                            if (i0 + qh < p.N) E::st(&dq_out[(long)qh * p.dq.n + c + (lane & 15)], tot);
                         }
                     }
                     // With two queries in a warp, lanes (q, delta) and (q + 1, delta + 1) own the same K2 row: the
@@ -1449,11 +1437,11 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
 #pragma unroll
                             for (int e = 0; e < CW / 2; ++e)
                                 rk[e] = __ffma2_rn(make_float2(__uint_as_float(g[2 * e]), __uint_as_float(g[2 * e + 1])),
-                                                   make_float2(bf16_lo(qw[e]), bf16_hi(qw[e])), rk[e]);
+                                                   make_float2(E::lo(qw[e]), E::hi(qw[e])), rk[e]);
 #pragma unroll
                             for (int e = 0; e < CW / 2; ++e)
                                 rv[e] = __ffma2_rn(make_float2(__uint_as_float(u[2 * e]), __uint_as_float(u[2 * e + 1])),
-                                                   make_float2(bf16_lo(ow[e]), bf16_hi(ow[e])), rv[e]);
+                                                   make_float2(E::lo(ow[e]), E::hi(ow[e])), rv[e]);
                         }
                         if (TWO_Q) __syncwarp();
                     }
@@ -1474,7 +1462,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                         float a = 0.f;
 #pragma unroll
                         for (int w = 0; w < WPQ; ++w) a += dq_part[(q2 * WPQ + w) * HALF + col];
-                        if (i0 + q2 < p.N) dq_out[(long)q2 * p.dq.n + col] = __float2bfloat16_rn(a);
+                        if (i0 + q2 < p.N) E::st(&dq_out[(long)q2 * p.dq.n + col], a);
                     }
                     named_barrier_sync(3 + grp, 128);     // before the next unit overwrites the partial rows
                 }
@@ -1518,7 +1506,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         {
             const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
             uint32_t nbf[2] = {0, 0}, g_base = 0, n_units = 0;
-            const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false);
+            const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false, F16);
             const uint32_t a_s = smem_base + L::kStat0, c_s = smem_base + L::kStat1;
             for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
                 const RowItem ri = row_item(P, it);
@@ -1538,7 +1526,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                         if (nbf[b] > 0) mbar_wait(&buf_free[b], (nbf[b] - 1) & 1, wctx, 39);
                         SA_TR(0, 3);
                         tc_fence_after();
-                        issue_sdp<HD>(leader, tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false));
+                        issue_sdp<HD>(leader, tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false, F16));
                         tc_commit(leader, &B.sdp_ready[b]);
                         if (t == ru.nt - 1) tc_commit(leader, B.stat_empty);     // A and C may be overwritten
                         ++nbf[b];
@@ -1571,7 +1559,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                         if (tp == 0 && n_units > 0) { mbar_wait(B.acc_free, (n_units - 1) & 1, wctx, 38); SA_TR(5, 6); }
                         tc_fence_after();
                         // U += P V1-tile ; G += dS K1-tile
-                        issue_acc<HD, true>(leader, tm_u, tm_g, tm_s[b], tm_dp[b], k1_t, v1_t, width / 16, tp > 0);
+                        issue_acc<HD, true, F16>(leader, tm_u, tm_g, tm_s[b], tm_dp[b], k1_t, v1_t, width / 16, tp > 0);
                         tc_commit(leader, &buf_free[b]);
                         tc_commit(leader, &B.st_empty[stage]);
                         SA_TR(5, 7);
@@ -1625,6 +1613,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
 // 4. dK2 / dV2 from the fp32 partials: sum over the query heads of a group, add the head partials of
 //    the runs that start within w2-1 queries after the row, convert to bf16.
 // ------------------------------------------------------------------------------------------------
+template <bool F16>
 __global__ void __launch_bounds__(256)
 kv2_reduce_kernel(BwdTcParams P, __nv_bfloat16* __restrict__ dk2, __nv_bfloat16* __restrict__ dv2) {
     const KParams& p = P.k;
@@ -1661,14 +1650,14 @@ kv2_reduce_kernel(BwdTcParams P, __nv_bfloat16* __restrict__ dk2, __nv_bfloat16*
         }
     }
     if (dk2) {
-        __nv_bfloat162* dst = (__nv_bfloat162*)(dk2 + b * p.dk2.b + (long)kb * p.dk2.n + hk * p.dk2.h + d);
-        dst[0] = __floats2bfloat162_rn(ak.x, ak.y);
-        dst[1] = __floats2bfloat162_rn(ak.z, ak.w);
+        uint32_t* dst = (uint32_t*)(dk2 + b * p.dk2.b + (long)kb * p.dk2.n + hk * p.dk2.h + d);
+        dst[0] = ptx::El<F16>::pack(ak.x, ak.y);
+        dst[1] = ptx::El<F16>::pack(ak.z, ak.w);
     }
     if (dv2) {
-        __nv_bfloat162* dst = (__nv_bfloat162*)(dv2 + b * p.dv2.b + (long)kb * p.dv2.n + hk * p.dv2.h + d);
-        dst[0] = __floats2bfloat162_rn(av.x, av.y);
-        dst[1] = __floats2bfloat162_rn(av.z, av.w);
+        uint32_t* dst = (uint32_t*)(dv2 + b * p.dv2.b + (long)kb * p.dv2.n + hk * p.dv2.h + d);
+        dst[0] = ptx::El<F16>::pack(av.x, av.y);
+        dst[1] = ptx::El<F16>::pack(av.z, av.w);
     }
 }
 
@@ -1709,10 +1698,12 @@ inline BwdPlan bwd_plan(const KParams& k, int sm_count) {
 
 inline size_t bwd_workspace_bytes(const KParams& k, int sm_count) { return bwd_plan(k, sm_count).total; }
 
-typedef bool (*MakeMapFn)(CUtensorMap*, const void*, int, int, int, int, const sa_strides&, int);
+typedef bool (*MakeMapFn)(CUtensorMap*, const void*, int, int, int, int, const sa_strides&, int, bool);
 
-// Returns an sa_status, or -1 when the tensor-core backward does not cover the problem.
-inline int launch_bwd(const KParams& k, const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
+// Returns an sa_status, or -1 when the tensor-core backward does not cover the problem.  F16: the tensors are
+// IEEE half instead of bf16.
+template <bool F16>
+inline int launch_bwd_t(const KParams& k, const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
                       const void* o, const float* lse, const void* d_o, void* dq, void* dk1, void* dk2, void* dv1,
                       void* dv2, uint8_t* workspace, DeviceStatus* status, cudaStream_t st, int* nlaunch, MakeMapFn make_map,
                       int sm_count, uint64_t wait_limit_ns) {
@@ -1738,24 +1729,24 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
     auto bf = [](const void* x) { return (const __nv_bfloat16*)x; };
 
     const long rows = (long)k.B * k.H * k.N;
-    prep_kernel<<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(k, bf(o), bf(d_o), lse, lse2, delta);
+    prep_kernel<F16><<<(unsigned)((rows + 3) / 4), 128, 0, st>>>(k, bf(o), bf(d_o), lse, lse2, delta);
     ++*nlaunch;
 
     const bool has_bias = k.k2_bias != 0.f || k.v2_bias != 0.f;     // selects the kernels that carry the bias adds
     if (dk1 || dv1) {
         CUtensorMap m1, m2;
-        if (!make_map(&m1, k1, k.B, k.n1, k.Hkv, k.D, k.k1, 128)) return SA_ERR_BAD_STRIDE;
-        if (!make_map(&m2, v1, k.B, k.n1, k.Hkv, k.D, k.v1, 128)) return SA_ERR_BAD_STRIDE;
+        if (!make_map(&m1, k1, k.B, k.n1, k.Hkv, k.D, k.k1, 128, F16)) return SA_ERR_BAD_STRIDE;
+        if (!make_map(&m2, v1, k.B, k.n1, k.Hkv, k.D, k.v1, 128, F16)) return SA_ERR_BAD_STRIDE;
         const long grid = P.num_col_items < sm_count ? P.num_col_items : sm_count;
         if (k.D == 128) {
-            auto kern = has_bias ? bwd_col_kernel<128, true> : bwd_col_kernel<128, false>;
+            auto kern = has_bias ? bwd_col_kernel<128, true, F16> : bwd_col_kernel<128, false, F16>;
             using LC = ColSmem<128>;
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LC::kAlloc) != cudaSuccess)
                 return SA_ERR_LAUNCH;
             kern<<<(unsigned)grid, kColThreads, LC::kAlloc, st>>>(P, m1, m2, bf(q), bf(k2), bf(v2), bf(d_o),
                                                                              (__nv_bfloat16*)dk1, (__nv_bfloat16*)dv1);
         } else {
-            auto kern = has_bias ? bwd_col_kernel<64, true> : bwd_col_kernel<64, false>;
+            auto kern = has_bias ? bwd_col_kernel<64, true, F16> : bwd_col_kernel<64, false, F16>;
             using LC = ColSmem<64>;
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, LC::kAlloc) != cudaSuccess)
                 return SA_ERR_LAUNCH;
@@ -1766,8 +1757,8 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
     }
     if (dq || dk2 || dv2) {
         CUtensorMap m1, m2;
-        if (!make_map(&m1, k1, k.B, k.n1, k.Hkv, k.D, k.k1, kStreamRows)) return SA_ERR_BAD_STRIDE;
-        if (!make_map(&m2, v1, k.B, k.n1, k.Hkv, k.D, k.v1, kStreamRows)) return SA_ERR_BAD_STRIDE;
+        if (!make_map(&m1, k1, k.B, k.n1, k.Hkv, k.D, k.k1, kStreamRows, F16)) return SA_ERR_BAD_STRIDE;
+        if (!make_map(&m2, v1, k.B, k.n1, k.Hkv, k.D, k.v1, kStreamRows, F16)) return SA_ERR_BAD_STRIDE;
         const long grid = P.num_row_items < sm_count ? P.num_row_items : sm_count;
         const int need_kv2 = (dk2 || dv2) ? 1 : 0;
         // shared-memory ring of fp32 dK2/dV2 rows beside the tiles: with the 3-stage K1/V1 ring if it fits,
@@ -1796,41 +1787,51 @@ inline int launch_bwd(const KParams& k, const void* q, const void* k1, const voi
             const bool fits5 = L3::kRing + 1024 + 2 * ring_want * 130 * 4 + kDqPart + stage5 <= L3::kMaxDynamic;
             const bool fits4 = L3::kRing + 1024 + 2 * ring_want * 130 * 4 + kDqPart + stage4 <= L3::kMaxDynamic;
             if (pl.dw_log2 == 5 && (fits5 || !need_kv2))     // separate epilogue warpgroups
-                ok = launch_row(has_bias ? bwd_row2_kernel<128, 5, 3, true> : bwd_row2_kernel<128, 5, 3, false>, L3::kRing, L3::kAlloc,
+                ok = launch_row(has_bias ? bwd_row2_kernel<128, 5, 3, true, F16> : bwd_row2_kernel<128, 5, 3, false, F16>, L3::kRing, L3::kAlloc,
                                 L3::kMaxDynamic, 128, kRow2Threads, kDqPart + stage5);
             else if (pl.dw_log2 == 4 && (fits4 || !need_kv2))
-                ok = launch_row(has_bias ? bwd_row2_kernel<128, 4, 3, true> : bwd_row2_kernel<128, 4, 3, false>, L3::kRing, L3::kAlloc,
+                ok = launch_row(has_bias ? bwd_row2_kernel<128, 4, 3, true, F16> : bwd_row2_kernel<128, 4, 3, false, F16>, L3::kRing, L3::kAlloc,
                                 L3::kMaxDynamic, 128, kRow2Threads, kDqPart + stage4);
             else if (pl.dw_log2 == 6 && (fits3x || !need_kv2))
-                ok = launch_row(has_bias ? bwd_row2_kernel<128, 6, 3, true> : bwd_row2_kernel<128, 6, 3, false>, L3::kRing, L3::kAlloc,
+                ok = launch_row(has_bias ? bwd_row2_kernel<128, 6, 3, true, F16> : bwd_row2_kernel<128, 6, 3, false, F16>, L3::kRing, L3::kAlloc,
                                 L3::kMaxDynamic, 128, kRow2Threads, kDqPart);
             else if (pl.dw_log2 == 6 && fits2)
-                ok = launch_row(has_bias ? bwd_row2_kernel<128, 6, 2, true> : bwd_row2_kernel<128, 6, 2, false>, L2::kRing, L2::kAlloc,
+                ok = launch_row(has_bias ? bwd_row2_kernel<128, 6, 2, true, F16> : bwd_row2_kernel<128, 6, 2, false, F16>, L2::kRing, L2::kAlloc,
                                 L2::kMaxDynamic, 128, kRow2Threads, kDqPart);
             else if (pl.dw_log2 == 4)
-                ok = launch_row(has_bias ? bwd_row_kernel<128, 3, true, true> : bwd_row_kernel<128, 3, true, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128);
+                ok = launch_row(has_bias ? bwd_row_kernel<128, 3, true, true, F16> : bwd_row_kernel<128, 3, true, false, F16>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128);
             else
-                ok = (fits3 || !need_kv2) ? launch_row(has_bias ? bwd_row_kernel<128, 3, false, true> : bwd_row_kernel<128, 3, false, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128)
-                                          : launch_row(has_bias ? bwd_row_kernel<128, 2, false, true> : bwd_row_kernel<128, 2, false, false>, L2::kRing, L2::kAlloc, L2::kMaxDynamic, 128);
+                ok = (fits3 || !need_kv2) ? launch_row(has_bias ? bwd_row_kernel<128, 3, false, true, F16> : bwd_row_kernel<128, 3, false, false, F16>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 128)
+                                          : launch_row(has_bias ? bwd_row_kernel<128, 2, false, true, F16> : bwd_row_kernel<128, 2, false, false, F16>, L2::kRing, L2::kAlloc, L2::kMaxDynamic, 128);
         } else {
             using L3 = BwdSmem<64, 3>;
             using L2 = BwdSmem<64, 2>;
             const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 66 * 4 <= L3::kMaxDynamic;
             if (pl.dw_log2 == 4)
-                ok = launch_row(has_bias ? bwd_row_kernel<64, 3, true, true> : bwd_row_kernel<64, 3, true, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64);
+                ok = launch_row(has_bias ? bwd_row_kernel<64, 3, true, true, F16> : bwd_row_kernel<64, 3, true, false, F16>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64);
             else
-                ok = (fits3 || !need_kv2) ? launch_row(has_bias ? bwd_row_kernel<64, 3, false, true> : bwd_row_kernel<64, 3, false, false>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64)
-                                          : launch_row(has_bias ? bwd_row_kernel<64, 2, false, true> : bwd_row_kernel<64, 2, false, false>, L2::kRing, L2::kAlloc, L2::kMaxDynamic, 64);
+                ok = (fits3 || !need_kv2) ? launch_row(has_bias ? bwd_row_kernel<64, 3, false, true, F16> : bwd_row_kernel<64, 3, false, false, F16>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64)
+                                          : launch_row(has_bias ? bwd_row_kernel<64, 2, false, true, F16> : bwd_row_kernel<64, 2, false, false, F16>, L2::kRing, L2::kAlloc, L2::kMaxDynamic, 64);
         }
         if (!ok) return SA_ERR_LAUNCH;
         ++*nlaunch;
         if (need_kv2) {
             const long total = (long)k.B * k.n2 * k.Hkv * (k.D / 4);
-            kv2_reduce_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(P, (__nv_bfloat16*)dk2, (__nv_bfloat16*)dv2);
+            kv2_reduce_kernel<F16><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(P, (__nv_bfloat16*)dk2, (__nv_bfloat16*)dv2);
             ++*nlaunch;
         }
     }
     return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
+}
+
+inline int launch_bwd(const KParams& k, const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
+                      const void* o, const float* lse, const void* d_o, void* dq, void* dk1, void* dk2, void* dv1,
+                      void* dv2, uint8_t* workspace, DeviceStatus* status, cudaStream_t st, int* nlaunch, MakeMapFn make_map,
+                      int sm_count, uint64_t wait_limit_ns, bool f16) {
+    return f16 ? launch_bwd_t<true>(k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2, workspace, status, st, nlaunch,
+                                    make_map, sm_count, wait_limit_ns)
+               : launch_bwd_t<false>(k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2, workspace, status, st, nlaunch,
+                                     make_map, sm_count, wait_limit_ns);
 }
 
 }  // namespace tc

@@ -121,8 +121,9 @@ __device__ __forceinline__ float2 exp2_poly2(float2 x) {
                        __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(xf.y) << 23)));
 }
 
-// BIAS = false: both biases are zero, every bias add folds away.
-template <int HD, bool BIAS>
+// BIAS = false: both biases are zero, every bias add folds away.  F16: the tensors are IEEE half instead of bf16
+// (same kernels; only the element encoding and the MMA's operand format differ).
+template <int HD, bool BIAS, bool F16 = false>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
               const __grid_constant__ CUtensorMap map_v1, const __nv_bfloat16* __restrict__ q,
@@ -130,6 +131,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
               __nv_bfloat16* __restrict__ o, float* __restrict__ lse) {
     using L = FwdSmem<HD>;
     using namespace ptx;
+    using E = El<F16>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t smem_base = smem_u32(smem);
@@ -242,8 +244,8 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
         {
             const int r = warp - 12;
             const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
-            const uint32_t idesc_pv = make_idesc(128, HD, false, true);
-            const uint32_t idesc_s_full = make_idesc(128, kSubTile, false, false);
+            const uint32_t idesc_pv = make_idesc(128, HD, false, true, F16);
+            const uint32_t idesc_s_full = make_idesc(128, kSubTile, false, false, F16);
             const uint32_t a_addr = smem_base + L::kA + r * L::kTileBytes;
             const uint32_t tmem_sb = tmem_base + 2 * r * kSubTile;     // this row tile's two S buffers
             uint32_t g = 0;          // ring position of the unit's first stage
@@ -259,7 +261,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                     mbar_wait(&k1_full[st], (gt / kStages) & 1, wctx, 3);
                     tc_fence_after();
                     const int b = (gs + sub) & 1;
-                    const uint32_t idesc_s = (sub == ug.nsub - 1) ? make_idesc(128, ug.last_width, false, false) : idesc_s_full;
+                    const uint32_t idesc_s = (sub == ug.nsub - 1) ? make_idesc(128, ug.last_width, false, false, F16) : idesc_s_full;
                     const uint64_t da = desc_kmajor(a_addr, 0);
                     const uint64_t db = desc_kmajor(smem_base + L::kK1 + st * L::kStageBytes, 0);
 #pragma unroll
@@ -351,9 +353,9 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
             uint8_t* tile_ = smem + L::kA + (R) * L::kTileBytes;                                                          \
             const int i0_ = (UG).i0 + (R) * qpt;                                                                          \
             if constexpr (DWL != 0) {                                                                                     \
-                store_product_tile_shared<HD, DWL, BIAS>(tile_, L::kSlabBytes, row, i0_, p.N, p.w2, p.halo2, FR, k2_bias); \
+                store_product_tile_shared<HD, DWL, BIAS, F16>(tile_, L::kSlabBytes, row, i0_, p.N, p.w2, p.halo2, FR, k2_bias); \
             } else {                                                                                                      \
-                form_product_tile<HD, 128, 128, BIAS>(tile_, L::kSlabBytes, row, (long)i0_ << P.dw_log2, P.dw_log2, p.N, p.w2, \
+                form_product_tile<HD, 128, 128, BIAS, F16>(tile_, L::kSlabBytes, row, (long)i0_ << P.dw_log2, P.dw_log2, p.N, p.w2, \
                                                       p.halo2, q + (UG).b * p.q.b + (UG).h * p.q.h, p.q.n,                \
                                                       k2 + (UG).b * p.k2.b + (UG).hk * p.k2.h, p.k2.n, k2_bias);          \
             }                                                                                                             \
@@ -446,7 +448,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                         for (int e = 0; e < 32; e += 2) {
                             // rows that are not valid have T = 0 exactly (their P is 0) and wrow = 0: no select needed
                             const uint32_t w = vw[e >> 1];
-                            float2 x2 = make_float2(bf16_lo(w), bf16_hi(w));
+                            float2 x2 = make_float2(E::lo(w), E::hi(w));
                             if (BIAS) x2 = __fadd2_rn(x2, make_float2(v2_bias, v2_bias));
                             const float2 y2 = __fmul2_rn(make_float2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])),
                                                          __fmul2_rn(x2, make_float2(wrow, wrow)));
@@ -462,7 +464,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                         if (i < p.N) {
                             __nv_bfloat16* orow = o + ug.b * p.o.b + (long)i * p.o.n + ug.h * p.o.h;
 #pragma unroll
-                            for (int cch = 0; cch < HD / 32; ++cch) orow[32 * cch + lane] = __float2bfloat16_rn(tot[cch]);
+                            for (int cch = 0; cch < HD / 32; ++cch) E::st(&orow[32 * cch + lane], tot[cch]);
                         }
                     } else {
 #pragma unroll
@@ -473,7 +475,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                             float acc = 0.f;
                             for (int w2i = 0; w2i < wpq; ++w2i) acc += part[(q2 * wpq + w2i) * HD + col];
                             const int i2 = ug.i0 + r * qpt + q2;
-                            if (i2 < p.N) o[ug.b * p.o.b + (long)i2 * p.o.n + ug.h * p.o.h + col] = __float2bfloat16_rn(acc);
+                            if (i2 < p.N) E::st(&o[ug.b * p.o.b + (long)i2 * p.o.n + ug.h * p.o.h + col], acc);
                         }
                         named_barrier_sync(1, kRowTile);
                     }
@@ -493,7 +495,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                         if (row_valid) load_bf16_words<16>(v2row + c0, vw16);
 #pragma unroll
                         for (int e = 0; e < 16; ++e) {
-                            const float vf = (e & 1) ? bf16_hi(vw16[e >> 1]) : bf16_lo(vw16[e >> 1]);
+                            const float vf = (e & 1) ? E::hi(vw16[e >> 1]) : E::lo(vw16[e >> 1]);
                             const float val = row_valid ? __uint_as_float(v[e]) * wrow * (vf + v2_bias) : 0.f;
                             scratch[row * 16 + (e ^ (row & 15))] = val;
                         }
@@ -506,7 +508,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                                 const int rr = (q2 << P.dw_log2) + d2;
                                 acc += scratch[rr * 16 + (e ^ (rr & 15))];
                             }
-                            if (i2 < p.N) o[ug.b * p.o.b + (long)i2 * p.o.n + ug.h * p.o.h + c0 + e] = __float2bfloat16_rn(acc);
+                            if (i2 < p.N) E::st(&o[ug.b * p.o.b + (long)i2 * p.o.n + ug.h * p.o.h + c0 + e], acc);
                         }
                         named_barrier_sync(1, kRowTile);
                     }
@@ -638,7 +640,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                         // column pairs take the polynomial.
                         const float2 pr = ((e >> 1) & 7) < SA_FWD_POLY_OF_8 ? exp2_poly2(x) : make_float2(ex2(x.x), ex2(x.y));
                         ls = __fadd2_rn(ls, pr);
-                        pk[e >> 1] = pack_bf16(pr.x, pr.y);
+                        pk[e >> 1] = E::pack(pr.x, pr.y);
                     }
                     // P (32 packed columns) overwrites the first half of the S buffer
                     tmem_st32(s_addr, pk);
@@ -677,7 +679,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                             p0 = (c >= lo && c <= hi) ? p0 : 0.f;
                             p1 = (c + 1 >= lo && c + 1 <= hi) ? p1 : 0.f;
                             lsum += p0 + p1;
-                            pk[e >> 1] = pack_bf16(p0, p1);
+                            pk[e >> 1] = E::pack(p0, p1);
                         }
                         tmem_st16(s_addr + (c0 >> 1), pk);
                     }

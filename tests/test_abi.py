@@ -65,6 +65,7 @@ def test_kernel_selection():
     assert r(D=64) == _abi.SA_ALGO_TCGEN05
     assert r(D=32) == _abi.SA_ALGO_GENERAL
     assert r(dtype=_abi.SA_F32) == _abi.SA_ALGO_GENERAL
+    assert r(dtype=_abi.SA_F16) == _abi.SA_ALGO_TCGEN05
     assert r(w2=200, N=4096) == _abi.SA_ALGO_GENERAL
     assert r(w2=200, N=64) == _abi.SA_ALGO_TCGEN05                           # window clipped to 64 rows
     assert r(algo=_abi.SA_ALGO_GENERAL) == _abi.SA_ALGO_GENERAL

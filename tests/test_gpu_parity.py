@@ -204,11 +204,40 @@ def test_edge_cases_finite(algo):
         host.default_algo = "auto"
 
 
-def test_fp16_and_fp32_use_general_kernels():
+def test_fp16_and_fp32_through_auto():
+    """The reference's dtype matrix (test_correctness.py:39,154): fp16 runs on the tensor-core kernels (where they
+    cover the shape), fp32 on the general kernels."""
     for dtype, tol in ((torch.float16, 1e-2), (torch.float32, 1e-4)):
         cfg, ins, outs = gu.load("tiny_sym")
         o, _, _ = _run(ins, cfg, "auto", dtype=dtype)
         assert float((o.float().cpu() - outs["o"]).abs().max()) <= tol
+
+
+@pytest.mark.parametrize("name", [n for n in gu.names() if _tc_supported(gu.load(n)[0])])
+def test_tensor_core_fp16_vs_reference_golden(name):
+    """IEEE half through the tensor-core kernels (the golden inputs are bf16 values, exact in half)."""
+    cfg, ins, outs = gu.load(name)
+    o, _, grads = _run(ins, cfg, "tcgen05", dtype=torch.float16)
+    assert o.dtype == torch.float16
+    assert float((o.float().cpu() - outs["o"]).abs().max()) <= TOL_O_BF16
+    for nm, g in zip(("dq", "dk1", "dk2", "dv1", "dv2"), grads):
+        assert g.dtype == torch.float16
+        assert _grad_err(g, outs[nm]) <= TOL_G_BF16, nm
+
+
+@pytest.mark.parametrize("case", [ORACLE_CASES[0], ORACLE_CASES[2], ORACLE_CASES[3], ORACLE_CASES[4], ORACLE_CASES[5], ORACLE_CASES[8]])
+def test_tensor_core_fp16_vs_cpu_oracle(case):
+    B, N, H, Hkv, D, w1, w2, kb, vb, h1, h2 = case
+    q, k1, k2, v1, v2, do = so.make_inputs(B, N, H, Hkv, D, seed=3, seed_do=4, halo1=h1, halo2=h2)
+    scale = 1.0 / math.sqrt(D)
+    cfg = dict(w1=w1, w2=w2, scale=scale, k2_bias=kb, v2_bias=vb)
+    ins = dict(q=q, k1=k1, k2=k2, v1=v1, v2=v2, do=do)
+    o, lse, grads = _run(ins, cfg, "tcgen05", dtype=torch.float16, halo1=h1, halo2=h2)
+    ref = so.forward_backward(q, k1, k2, v1, v2, do, w1, w2, scale, kb, vb, h1, h2)
+    assert float((o.float().cpu() - ref[0]).abs().max()) <= TOL_O_BF16
+    assert float((lse.cpu() - ref[1]).abs().max()) <= 2e-2
+    for nm, g, r in zip(("dq", "dk1", "dk2", "dv1", "dv2"), grads, ref[2:]):
+        assert _grad_err(g, r) <= TOL_G_BF16, nm
 
 
 def test_bad_arguments_raise():
