@@ -94,36 +94,39 @@ class _StatusWatch:
     SLOTS = 32                      # pinned status slots per device, reused
 
     def __init__(self):
-        self._dev = {}              # device index -> (pinned [SLOTS, 4] int32, free slot list, pending list, stream)
+        self._dev = {}              # device index -> (pinned [SLOTS, 4] int32, free slots, pending, stream, device [SLOTS, 4] int32)
 
     def _state(self, index: int):
         st = self._dev.get(index)
         if st is None:
+            dev = torch.device("cuda", index)
             st = (torch.zeros(self.SLOTS, 4, dtype=torch.int32).pin_memory(), list(range(self.SLOTS)), [],
-                  torch.cuda.Stream(torch.device("cuda", index)))
+                  torch.cuda.Stream(dev), torch.empty(self.SLOTS, 4, dtype=torch.int32, device=dev))
             self._dev[index] = st
         return st
 
     def watch(self, ws: torch.Tensor, label: str) -> None:
-        host, free, pending, side = self._state(ws.device.index)
+        host, free, pending, side, small = self._state(ws.device.index)
         if not free:
             self.poll(ws.device, wait_oldest=True)
         i = free.pop()
-        # The copy runs on a stream of its own, after the work issued so far: a device-to-host copy on
-        # the caller's stream would queue behind whatever large transfers keep the copy engines busy and
-        # hold the caller's next kernels back.
-        side.wait_stream(torch.cuda.current_stream(ws.device))
+        # The status word first goes to a small device slot, on the caller's stream (16 bytes, device to device),
+        # so that the workspace itself is not held any longer than the kernels need it.  The device-to-host copy
+        # then runs on a stream of its own: on the caller's stream it would queue behind whatever large transfers
+        # keep the copy engines busy and hold the caller's next kernels back.
+        cur = torch.cuda.current_stream(ws.device)
+        small[i].copy_(ws[:16].view(torch.int32))
+        side.wait_stream(cur)
         with torch.cuda.stream(side):
-            host[i].copy_(ws[:16].view(torch.int32), non_blocking=True)
+            host[i].copy_(small[i], non_blocking=True)
             ev = torch.cuda.Event()
             ev.record(side)
-        ws.record_stream(side)
         pending.append((ev, i, label))
 
     def poll(self, device: torch.device, wait: bool = False, wait_oldest: bool = False) -> None:
         if device.index not in self._dev:
             return
-        host, free, pending, _ = self._state(device.index)
+        host, free, pending, _, _ = self._state(device.index)
         bad = None
         keep = []
         for n, (ev, i, label) in enumerate(pending):
