@@ -1127,11 +1127,12 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 }
 
 // ------------------------------------------------------------------------------------------------
-// 3b. Row kernel with separate epilogue warpgroups, for 16, 32 or 64 delta slots per query (w2 in 9..64) when
-//     the dK2/dV2 ring fits: warps 0-7 form the operands and run the softmax, warps 8-15 read U and G
-//     out of tensor memory (dQ, dK2 ring, dV2 ring) while warps 0-7 already work on the next unit, so
-//     the epilogue of a unit overlaps the main loop of the next one.  Same math, same order of
-//     additions, same workspace contents as bwd_row_kernel.
+// 3b. Row kernel with separate operand / epilogue warpgroups, for 16, 32 or 64 delta slots per query (w2 in
+//     9..64) when the dK2/dV2 ring fits: warps 0-7 run the softmax of every tile, warps 8-15 form the next
+//     unit's operands the moment the tensor cores have finished with the current ones and take U and G out of
+//     tensor memory (dQ, dK2 ring, dV2 ring) while warps 0-7 already work on the next unit, so neither the
+//     operand formation nor the epilogue of a unit interrupts the stream of tiles.  Same workspace contents as
+//     bwd_row_kernel; U and G pass through one 16-bit rounding before the final sums.
 // ------------------------------------------------------------------------------------------------
 // Bytes of one staging buffer of the row kernel with separate epilogue warpgroups: the raw Q and dO rows of a
 // unit's queries and the K2 rows of their window (row pitch padded by 16 bytes so that the lanes of a warp, which
@@ -1140,6 +1141,13 @@ constexpr int row2_stage_bytes(int dwl, int hd) {
     return dwl > 5 ? 0 : 2 * (128 >> dwl) * hd * 2 + ((1 << dwl) + (128 >> dwl) - 1) * (hd * 2 + 16);
 }
 
+#ifndef SA_R2_SM
+#define SA_R2_SM 104
+#define SA_R2_EP 112
+#endif
+#ifndef SA_R2_REST
+#define SA_R2_REST 48
+#endif
 constexpr int kRow2Threads = 640;     // softmax groups (0-7), epilogue groups (8-15), MMA issuers (16, 17), TMA (18), 1 idle
 
 template <int HD, int DWL, int NS, bool BIAS, bool F16 = false>
@@ -1163,11 +1171,9 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
     const KParams& p = P.k;
     const BwdBars B = bwd_bars<NS>((uint64_t*)(smem + L::kBars));
     uint64_t* const buf_free = (uint64_t*)(smem + L::kBars) + 2 * NS + 8;      // [2] an S / dP buffer's P and dS have been consumed
-    uint64_t* const stg_full = buf_free + 2;                                  // [2] staging buffer written (softmax groups -> epilogue groups)
-    uint64_t* const stg_free = buf_free + 4;                                  // [2] staging buffer read (epilogue groups -> softmax groups)
-    // Staging: the softmax groups have a unit's Q, dO and K2 rows in registers when they form A and C; they leave
-    // raw copies in shared memory for the epilogue groups, which would otherwise fetch the same rows from global
-    // memory in every phase, with the latency of those loads on the path that frees the accumulators.
+    // Staging: the groups that form A and C have a unit's Q, dO and K2 rows in registers then; they leave raw copies in
+    // shared memory (two buffers, alternating by unit) for the unit's epilogue, which needs the same rows again per
+    // column chunk and would otherwise fetch them from global memory.
     constexpr bool STAGE = DWL <= 5;
     constexpr int NWIN = DW + QPT - 1;
     constexpr int K2PITCH = HD * 2 + 16;
@@ -1190,14 +1196,12 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
             mbar_init(&B.sdp_ready[b], 1);
             mbar_init(&B.pds_ready[b], 8);     // both softmax groups: each turns half the columns of a tile into P and dS
         }
-        mbar_init(B.stat_full, 8);         // A and C formed by the two softmax groups
+        mbar_init(B.stat_full, 8);         // A and C formed by the two operand / epilogue groups
         mbar_init(B.stat_empty, 1);        // the unit's last S / dP MMAs have read A and C
         mbar_init(B.acc_ready, 1);         // U and G final
         mbar_init(B.acc_free, 8);          // U and G read out by the two epilogue groups
         for (int b = 0; b < 2; ++b) {
             mbar_init(&buf_free[b], 1);
-            mbar_init(&stg_full[b], 8);
-            mbar_init(&stg_free[b], 8);
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -1214,125 +1218,79 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
     const uint32_t tm_dp[2] = {tmem_base + 128, tmem_base + 192};
     const uint32_t tm_u = tmem_base + 256, tm_g = tmem_base + 384;     // U = P V1, G = dS K1
 
-    // Register pool of the block: 640 x 96 = 2 x 120 (softmax groups) + 2 x 96 (epilogue groups) + 48 (the
-    // rest): an increase beyond the block's own pool would never return.
+    // Register pool of the block: 640 x 96 = 128 x (2 x 104 (softmax groups) + 2 x 112 (operand / epilogue groups) +
+    // 48 (the rest)): an increase beyond the block's own pool would never return.
     if (warp < 8) {
-        // ---------------------------------------------------------------- operand formation + softmax
-        // Group 0 forms A = Q * K2, group 1 forms C = dO * V2.  Every column tile (64 columns) is split
-        // between the groups: group g turns columns [32g, 32g + 32) of S and dP into P and dS, so a tile's
-        // softmax takes half as long and the accumulating MMAs that wait for it start that much earlier.
-        // P and dS (bf16) go to columns [32g, 32g + 16) of the S / dP buffer: inside the group's own columns.
-        reg_alloc<120>();
+        // ---------------------------------------------------------------- softmax
+        // Every column tile (64 columns) is split between the two groups: group g turns columns [32g, 32g + 32)
+        // of S and dP into P and dS, so a tile's softmax takes half as long and the accumulating MMAs that wait
+        // for it start that much earlier.  P and dS (16-bit) go to columns [32g, 32g + 16) of the S / dP buffer:
+        // inside the group's own columns.  The two S / dP buffers alternate over all tiles of the block, not per
+        // unit, so that the first tile of a unit never waits for the buffer of the previous unit's last tile.
+        reg_alloc<SA_R2_SM>();
         const int grp = warp >> 2;
         const int row = tid & 127;
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
         const int qq = row >> DWL;
         const int dlt = row & (DW - 1);
         const float c2 = p.scale * kLog2e;
-        uint8_t* my_tile = smem + (grp == 0 ? L::kStat0 : L::kStat1);      // group 0 forms A, group 1 forms C
         auto warp_arrive = [&](uint64_t* bar) {      // every lane has finished and fenced its part; lane 0 arrives for the warp
             __syncwarp();
             if (lane == 0) mbar_arrive(bar);
         };
-        const __nv_bfloat16* const x_t = grp == 0 ? q : d_o;               // row operand of this group's tile
-        const __nv_bfloat16* const y_t = grp == 0 ? k2 : v2;               // window operand
-        const sa_strides xs = grp == 0 ? p.q : p.d_o, ys = grp == 0 ? p.k2 : p.v2;
-        const float bias = BIAS ? (grp == 0 ? p.k2_bias : p.v2_bias) : 0.f;
-        uint4 fr[ProductTileShape<HD, DWL>::NREGS];  // the unit's operand rows, loaded one unit ahead
-        uint32_t nb[2] = {0, 0}, n_units = 0;
-        long it = blockIdx.x;
-        RowItem ri = row_item(P, it < P.num_row_items ? it : 0);
-        int i0 = ri.i_run0;
-        if (it < P.num_row_items)
-            load_product_tile_shared<HD, DWL>(fr, row, i0, p.N, p.halo2, x_t + ri.b * xs.b + ri.h * xs.h, xs.n,
-                                              y_t + ri.b * ys.b + ri.hk * ys.h, ys.n);
-        while (it < P.num_row_items) {
-            const RowUnit ru = row_unit(P, i0);
-            const int i = i0 + qq;
-            const int kb = i + p.halo2 - dlt;
-            const bool row_valid = (i < p.N) && (dlt < p.w2) && (kb >= 0);
-            const int ic = min(i, p.N - 1);
-            // ---- stationary operand of this group, once the previous unit's S / dP MMAs have read the old one
-            if (n_units > 0) mbar_wait(B.stat_empty, (n_units - 1) & 1, wctx, 37);
-            if ((warp & 3) == 0) SA_TR(1 + grp, 50);
-            SA_PROF_T0(t_form);
-            store_product_tile_shared<HD, DWL, BIAS, F16>(my_tile, L::kBigSlab, row, i0, p.N, p.w2, p.halo2, fr, bias);
-            if constexpr (STAGE) {
-                using S = ProductTileShape<HD, DWL>;
-                const int sb = n_units & 1;                              // this unit's staging buffer; its (n_units >> 1)-th use
-                if (n_units >= 2) mbar_wait(&stg_free[sb], ((n_units >> 1) - 1) & 1, wctx, 40);
-                uint8_t* const stg = stage_base + sb * kStageBuf;
-                const int c = row % S::C, pr = row / S::C;
-                if (pr == 0) {                                           // Q rows (group 0) / dO rows (group 1)
-#pragma unroll
-                    for (int q2 = 0; q2 < S::NQ; ++q2) *(uint4*)(stg + (grp * QPT + q2) * HD * 2 + c * 16) = fr[q2];
-                }
-                if (grp == 0) {                                          // the K2 rows of the unit's window
-#pragma unroll
-                    for (int k = 0; k < S::PASSES; ++k) {
-                        const int w = pr + k * S::RPP;
-                        if (w < NWIN) *(uint4*)(stg + 2 * QPT * HD * 2 + w * K2PITCH + c * 16) = fr[S::NQ + k];
+        uint32_t gt = 0;                             // tiles so far
+        for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
+            const RowItem ri = row_item(P, it);
+            for (int i0 = ri.i_run0; i0 < ri.i_run1; i0 += QPT) {
+                const RowUnit ru = row_unit(P, i0);
+                const int i = i0 + qq;
+                const int kb = i + p.halo2 - dlt;
+                const bool row_valid = (i < p.N) && (dlt < p.w2) && (kb >= 0);
+                const int ic = min(i, p.N - 1);
+                SA_PROF_T0(t_loop);
+                const long li = ((long)ri.b * p.H + ri.h) * p.N + ic;
+                const float lse2 = P.lse2[li], dlt_i = P.delta[li];
+                const int jhi = row_valid ? i + p.halo1 : -1;
+                const int jlo = row_valid ? max(0, i + p.halo1 - p.w1 + 1) : 0;
+                for (int t = 0; t < ru.nt; ++t, ++gt) {
+                    const int b = gt & 1;
+                    const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
+                    const int c0 = 32 * grp;                                   // first column of this group's half
+                    const int tile0 = ru.col_start + t * kStreamRows;
+                    const int lo = jlo - tile0, hi = jhi - tile0;
+                    const bool full = __all_sync(0xffffffffu, lo <= c0 && hi >= c0 + 31);
+                    mbar_wait(&B.sdp_ready[b], (gt >> 1) & 1, wctx, 30);
+                    if ((warp & 3) == 0) SA_TR(1 + grp, 52);
+                    tc_fence_after();
+                    SA_PROF_T0(t_rsm);
+                    if (c0 < width) {
+                        uint32_t s[32], dp[32], pp[16], ds[16];
+                        tmem_ld32(tm_s[b] + lane_addr + c0, s);
+                        tmem_ld32(tm_dp[b] + lane_addr + c0, dp);
+                        tmem_wait_ld();
+                        if (full) softmax_bwd_chunk<false, 32, F16>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
+                        else softmax_bwd_chunk<true, 32, F16>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
+                        tmem_st16(tm_s[b] + lane_addr + c0, pp);
+                        tmem_st16(tm_dp[b] + lane_addr + c0, ds);
+                        tmem_wait_st();
                     }
+                    tc_fence_before();
+                    warp_arrive(&B.pds_ready[b]);
+                    if ((warp & 3) == 0) SA_TR(1 + grp, 53);
+                    SA_PROF_ADD(58 + grp, t_rsm);
                 }
-                warp_arrive(&stg_full[sb]);
+                SA_PROF_ADD(42 + grp, t_loop);
             }
-            fence_proxy_async_smem();
-            tc_fence_before();
-            warp_arrive(B.stat_full);
-            if ((warp & 3) == 0) SA_TR(1 + grp, 51);
-            SA_PROF_ADD(40 + grp, t_form);
-            SA_PROF_T0(t_loop);
-            const long li = ((long)ri.b * p.H + ri.h) * p.N + ic;
-            const float lse2 = P.lse2[li], dlt_i = P.delta[li];
-            const int jhi = row_valid ? i + p.halo1 : -1;
-            const int jlo = row_valid ? max(0, i + p.halo1 - p.w1 + 1) : 0;
-            // ---- this group's half of every column tile
-            for (int t = 0; t < ru.nt; ++t) {
-                const int b = t & 1;
-                const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
-                const int c0 = 32 * grp;                                   // first column of this group's half
-                const int tile0 = ru.col_start + t * kStreamRows;
-                const int lo = jlo - tile0, hi = jhi - tile0;
-                const bool full = __all_sync(0xffffffffu, lo <= c0 && hi >= c0 + 31);
-                mbar_wait(&B.sdp_ready[b], nb[b] & 1, wctx, 30);
-                ++nb[b];
-                if ((warp & 3) == 0) SA_TR(1 + grp, 52);
-                tc_fence_after();
-                SA_PROF_T0(t_rsm);
-                if (c0 < width) {
-                    uint32_t s[32], dp[32], pp[16], ds[16];
-                    tmem_ld32(tm_s[b] + lane_addr + c0, s);
-                    tmem_ld32(tm_dp[b] + lane_addr + c0, dp);
-                    tmem_wait_ld();
-                    if (full) softmax_bwd_chunk<false, 32, F16>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
-                    else softmax_bwd_chunk<true, 32, F16>(s, dp, c0, lo, hi, c2, lse2, dlt_i, pp, ds);
-                    tmem_st16(tm_s[b] + lane_addr + c0, pp);
-                    tmem_st16(tm_dp[b] + lane_addr + c0, ds);
-                    tmem_wait_st();
-                }
-                tc_fence_before();
-                warp_arrive(&B.pds_ready[b]);
-                if ((warp & 3) == 0) SA_TR(1 + grp, 53);
-                SA_PROF_ADD(58 + grp, t_rsm);
-            }
-            SA_PROF_ADD(42 + grp, t_loop);
-            // ---- next unit; its operand rows start travelling now (always some unit's rows, so that the registers
-            // are defined on every path)
-            ++n_units;
-            i0 += QPT;
-            if (i0 >= ri.i_run1) {
-                it += gridDim.x;
-                ri = row_item(P, it < P.num_row_items ? it : it - gridDim.x);
-                i0 = ri.i_run0;
-            }
-            load_product_tile_shared<HD, DWL>(fr, row, i0, p.N, p.halo2, x_t + ri.b * xs.b + ri.h * xs.h, xs.n,
-                                              y_t + ri.b * ys.b + ri.hk * ys.h, ys.n);
         }
     } else if (warp < 16) {
-        // ---------------------------------------------------------------- epilogue groups: group g takes columns
-        // [g * HD/2, (g + 1) * HD/2) of all three results (dQ and dK2 from G, dV2 from U), so both groups
-        // carry the same load and no ring column is shared between them
-        // (these groups keep the 96 registers the block was launched with)
+        // ---------------------------------------------------------------- operand + epilogue groups
+        // Two jobs, interleaved per unit.  (1) Form the NEXT unit's stationary operands as soon as the current
+        // unit's last S / dP MMAs have read the old ones: group 0 forms A = Q * K2, group 1 forms C = dO * V2, from
+        // rows loaded well before (the softmax groups are still busy with the current unit's last tiles then, and
+        // the S / dP MMAs of the next unit can follow the current unit's without a gap).  (2) The current unit's
+        // epilogue: group g takes columns [g * HD/2, (g + 1) * HD/2) of all three results (dQ and dK2 from G, dV2
+        // from U), so both groups carry the same load and no ring column is shared between them.
+        reg_alloc<SA_R2_EP>();
         const int grp = (warp - 8) >> 2;
         const int row = tid & 127;
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
@@ -1354,11 +1312,74 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
             ring_v[idx] = 0.f;
         }
         named_barrier_sync(3 + grp, 128);
+        // ---- operand formation: this group's tile, its row and window operands
+        uint8_t* const my_tile = smem + (grp == 0 ? L::kStat0 : L::kStat1);
+        const __nv_bfloat16* const x_t = grp == 0 ? q : d_o;
+        const __nv_bfloat16* const y_t = grp == 0 ? k2 : v2;
+        const sa_strides xs = grp == 0 ? p.q : p.d_o, ys = grp == 0 ? p.k2 : p.v2;
+        const float bias = BIAS ? (grp == 0 ? p.k2_bias : p.v2_bias) : 0.f;
+        // Forms the unit that starts at query f_i0 of item f_ri out of the rows in fr; leaves raw copies of the Q, dO
+        // and K2 rows in staging buffer sb for the epilogue (which needs them again, per column chunk).
+        long f_it = blockIdx.x;                            // the unit to form next
+        RowItem f_ri = row_item(P, f_it < P.num_row_items ? f_it : 0);
+        int f_i0 = f_ri.i_run0;
+        uint32_t n_formed = 0;
+#define SA_ROW2_LOAD(fr)                                                                                              \
+        load_product_tile_shared<HD, DWL>(fr, row, f_i0, p.N, p.halo2, x_t + f_ri.b * xs.b + f_ri.h * xs.h, xs.n,      \
+                                          y_t + f_ri.b * ys.b + f_ri.hk * ys.h, ys.n)
+#define SA_ROW2_FORM(fr)                                                                                              \
+        do {                                                                                                          \
+            using S = ProductTileShape<HD, DWL>;                                                                      \
+            if ((warp & 3) == 0) SA_TR(3 + grp, 50);                                                                  \
+            store_product_tile_shared<HD, DWL, BIAS, F16>(my_tile, L::kBigSlab, row, f_i0, p.N, p.w2, p.halo2, fr, bias); \
+            if constexpr (STAGE) {                                                                                    \
+                uint8_t* const stg_w = stage_base + (n_formed & 1) * kStageBuf;                                       \
+                const int c = row % S::C, pr = row / S::C;                                                            \
+                if (pr == 0) {                                                                                        \
+                    _Pragma("unroll") for (int q2 = 0; q2 < S::NQ; ++q2)                                              \
+                        *(uint4*)(stg_w + (grp * QPT + q2) * HD * 2 + c * 16) = fr[q2];                               \
+                }                                                                                                     \
+                if (grp == 0) {                                                                                       \
+                    _Pragma("unroll") for (int k = 0; k < S::PASSES; ++k) {                                           \
+                        const int w = pr + k * S::RPP;                                                                \
+                        if (w < NWIN) *(uint4*)(stg_w + 2 * QPT * HD * 2 + w * K2PITCH + c * 16) = fr[S::NQ + k];     \
+                    }                                                                                                 \
+                }                                                                                                     \
+            }                                                                                                         \
+            fence_proxy_async_smem();                                                                                 \
+            tc_fence_before();                                                                                        \
+            __syncwarp();                                                                                             \
+            if (lane == 0) mbar_arrive(B.stat_full);                                                                  \
+            if ((warp & 3) == 0) SA_TR(3 + grp, 51);                                                                  \
+            ++n_formed;                                                                                               \
+            f_i0 += QPT;                                                                                              \
+            if (f_i0 >= f_ri.i_run1) {                                                                                \
+                f_it += gridDim.x;                                                                                    \
+                f_ri = row_item(P, f_it < P.num_row_items ? f_it : f_it - gridDim.x);                                 \
+                f_i0 = f_ri.i_run0;                                                                                   \
+            }                                                                                                         \
+        } while (0)
+        if (f_it < P.num_row_items) {
+            uint4 fr[ProductTileShape<HD, DWL>::NREGS];
+            SA_ROW2_LOAD(fr);
+            SA_ROW2_FORM(fr);
+        }
         int flush_lo = 0;
         uint32_t n_units = 0;
         for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
             const RowItem ri = row_item(P, it);
             for (int i0 = ri.i_run0, uidx = 0; i0 < ri.i_run1; i0 += QPT, ++uidx, ++n_units) {
+                {
+                    // the next unit's operands (always some unit's rows, so that the loop has one shape); both groups
+                    // meet first: the staging buffer about to be rewritten was read by both in the unit before last
+                    uint4 fr[ProductTileShape<HD, DWL>::NREGS];
+                    SA_ROW2_LOAD(fr);
+                    named_barrier_sync(5, 256);
+                    if (f_it < P.num_row_items) {
+                        mbar_wait(B.stat_empty, n_units & 1, wctx, 37);      // this unit's last S / dP MMAs have read A and C
+                        SA_ROW2_FORM(fr);
+                    }
+                }
                 const int i = i0 + qq;
                 const int kb = i + p.halo2 - dlt;
                 const bool row_valid = (i < p.N) && (dlt < p.w2) && (kb >= 0);
@@ -1373,43 +1394,82 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                 const int slot = row_valid ? kb % max(ring_rows, 1) : 0;
                 __nv_bfloat16* dq_out = dq == nullptr ? nullptr : dq + ri.b * p.dq.b + (long)i0 * p.dq.n + ri.h * p.dq.h + cbase;
                 const uint8_t* stg = nullptr;
-                if constexpr (STAGE) {
-                    const int sb = n_units & 1;
-                    mbar_wait(&stg_full[sb], (n_units >> 1) & 1, wctx, 41);
-                    stg = stage_base + sb * kStageBuf;
-                }
+                if constexpr (STAGE) stg = stage_base + (n_units & 1) * kStageBuf;
                 const int wrow_k2 = qq + DW - 1 - dlt;                       // this lane's K2 row inside the unit's window
                 mbar_wait(B.acc_ready, n_units & 1, wctx, 31);
                 if ((warp & 3) == 0) SA_TR(3 + grp, 60);
                 tc_fence_after();
                 SA_PROF_T0(t_epi);
-                // A warp holds the 32 deltas of one query (or the 16 deltas of two): within a query the lanes own distinct K2 rows.  Warp w works
-                // on column chunk (w + phase) % 4 of the group's half, so no two warps touch the same ring columns
-                // at the same time; the delta sum for dQ is a register exchange inside the warp.  Rows that are
-                // not valid have P = dS = 0, hence exact zeros in U and G: they need no masking in the sums.
-#pragma unroll 1
+                // U and G leave tensor memory at once, as packed 16-bit pairs held in registers (half the group's columns
+                // of both, 64 registers), and the accumulators are handed back to the MMA issuer before any of the sums
+                // below: those take several thousand cycles per unit, during which the next unit's accumulating MMAs
+                // would otherwise stand still.  The rounding is that of the results themselves (one 16-bit rounding
+                // of every addend, before sums of at most w2 of them).
+                // A warp holds the 32 deltas of one query (or the 16 deltas of two): within a query the lanes own distinct
+                // K2 rows.  In phase ph warp w works on column chunk (w + ph) % 4 of the group's half, so no two warps
+                // touch the same ring columns at the same time; register slot ph holds that chunk.  Rows that are not
+                // valid have P = dS = 0, hence exact zeros in U and G: they need no masking in the sums.
+                uint32_t gp[NPHG][CW / 2], up[NPHG][CW / 2];
+#pragma unroll
                 for (int ph = 0; ph < NPHG; ++ph) {
                     const int c = ((wq + ph) & 3) * CW;
-                    uint32_t qw[CW / 2], ow[CW / 2], xw[CW / 2], g[CW], u[CW];
-                    if constexpr (STAGE) {
-                        load_bf16_words<CW>((const __nv_bfloat16*)(stg + qq * HD * 2) + cbase + c, qw);
-                        load_bf16_words<CW>((const __nv_bfloat16*)(stg + (QPT + qq) * HD * 2) + cbase + c, ow);
-                        load_bf16_words<CW>((const __nv_bfloat16*)(stg + 2 * QPT * HD * 2 + wrow_k2 * K2PITCH) + cbase + c, xw);
-                    } else {
-                        load_bf16_words<CW>(q_row + c, qw);
-                        load_bf16_words<CW>(do_row + c, ow);
-                        load_bf16_words<CW>(k2_row + c, xw);
-                    }
+                    uint32_t g[CW], u[CW];
                     tmem_ld16(tm_g + lane_addr + cbase + c, g);
                     tmem_ld16(tm_u + lane_addr + cbase + c, u);
                     tmem_wait_ld();
+#pragma unroll
+                    for (int e = 0; e < CW / 2; ++e) {
+                        gp[ph][e] = El<false>::pack(__uint_as_float(g[2 * e]), __uint_as_float(g[2 * e + 1]));
+                        up[ph][e] = El<false>::pack(__uint_as_float(u[2 * e]), __uint_as_float(u[2 * e + 1]));
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(B.acc_free);        // the next unit's accumulating MMAs may start
+                if ((warp & 3) == 0) SA_TR(3 + grp, 61);
+                // ---- dV2 from U
+                if (need_kv2) {
+#pragma unroll
+                    for (int ph = 0; ph < NPHG; ++ph) {
+                        const int c = ((wq + ph) & 3) * CW;
+                        uint32_t ow[CW / 2];
+                        if constexpr (STAGE) load_bf16_words<CW>((const __nv_bfloat16*)(stg + (QPT + qq) * HD * 2) + cbase + c, ow);
+                        else load_bf16_words<CW>(do_row + c, ow);
+#pragma unroll
+                        for (int turn = 0; turn < (TWO_Q ? 2 : 1); ++turn) {
+                            // with two queries in a warp, lanes (q, delta) and (q + 1, delta + 1) own the same row: the halves take turns
+                            if (row_valid && (!TWO_Q || (lane >> 4) == turn)) {
+                                float2* rv = (float2*)(ring_v + ring_index<HD>(slot, cbase + c));
+#pragma unroll
+                                for (int e = 0; e < CW / 2; ++e)
+                                    rv[e] = __ffma2_rn(make_float2(El<false>::lo(up[ph][e]), El<false>::hi(up[ph][e])),
+                                                       make_float2(E::lo(ow[e]), E::hi(ow[e])), rv[e]);
+                            }
+                            if (TWO_Q) __syncwarp();
+                        }
+                        named_barrier_sync(3 + grp, 128);
+                    }
+                }
+                if ((warp & 3) == 0) SA_TR(3 + grp, 62);
+                // ---- dQ and dK2 from G
+#pragma unroll
+                for (int ph = 0; ph < NPHG; ++ph) {
+                    const int c = ((wq + ph) & 3) * CW;
+                    uint32_t qw[CW / 2], xw[CW / 2];
+                    if constexpr (STAGE) {
+                        load_bf16_words<CW>((const __nv_bfloat16*)(stg + qq * HD * 2) + cbase + c, qw);
+                        load_bf16_words<CW>((const __nv_bfloat16*)(stg + 2 * QPT * HD * 2 + wrow_k2 * K2PITCH) + cbase + c, xw);
+                    } else {
+                        load_bf16_words<CW>(q_row + c, qw);
+                        load_bf16_words<CW>(k2_row + c, xw);
+                    }
                     if (dq != nullptr) {
                         float v[CW];
 #pragma unroll
                         for (int e = 0; e < CW; e += 2) {
                             float2 x2 = make_float2(E::lo(xw[e >> 1]), E::hi(xw[e >> 1]));
                             if (BIAS) x2 = __fadd2_rn(x2, make_float2(p.k2_bias, p.k2_bias));
-                            const float2 t = __fmul2_rn(make_float2(__uint_as_float(g[e]), __uint_as_float(g[e + 1])), x2);
+                            const float2 t = __fmul2_rn(make_float2(El<false>::lo(gp[ph][e >> 1]), El<false>::hi(gp[ph][e >> 1])), x2);
                             v[e] = t.x;
                             v[e + 1] = t.y;
                         }
@@ -1427,34 +1487,20 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                             if (i0 + qh < p.N) E::st(&dq_out[(long)qh * p.dq.n + c + (lane & 15)], tot);
                         }
                     }
-                    // With two queries in a warp, lanes (q, delta) and (q + 1, delta + 1) own the same K2 row: the
-                    // halves take turns.
 #pragma unroll
                     for (int turn = 0; turn < (TWO_Q ? 2 : 1); ++turn) {
                         if (need_kv2 && row_valid && (!TWO_Q || (lane >> 4) == turn)) {
                             float2* rk = (float2*)(ring_k + ring_index<HD>(slot, cbase + c));
-                            float2* rv = (float2*)(ring_v + ring_index<HD>(slot, cbase + c));
 #pragma unroll
                             for (int e = 0; e < CW / 2; ++e)
-                                rk[e] = __ffma2_rn(make_float2(__uint_as_float(g[2 * e]), __uint_as_float(g[2 * e + 1])),
+                                rk[e] = __ffma2_rn(make_float2(El<false>::lo(gp[ph][e]), El<false>::hi(gp[ph][e])),
                                                    make_float2(E::lo(qw[e]), E::hi(qw[e])), rk[e]);
-#pragma unroll
-                            for (int e = 0; e < CW / 2; ++e)
-                                rv[e] = __ffma2_rn(make_float2(__uint_as_float(u[2 * e]), __uint_as_float(u[2 * e + 1])),
-                                                   make_float2(E::lo(ow[e]), E::hi(ow[e])), rv[e]);
                         }
                         if (TWO_Q) __syncwarp();
                     }
                     named_barrier_sync(3 + grp, 128);
-                    if ((warp & 3) == 0) SA_TR(3 + grp, 61 + ph);
                 }
-                // U / G have been read: the next unit's accumulating MMAs may start
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(B.acc_free);
-                    if constexpr (STAGE) mbar_arrive(&stg_free[n_units & 1]);      // ... and the staging buffer may be rewritten
-                }
+                if ((warp & 3) == 0) SA_TR(3 + grp, 65);
                 if (WPQ > 1 && dq != nullptr) {
                     // a query spans WPQ warps: add their partial rows (the last phase ended with a barrier)
                     for (int idx = row; idx < QPT * HALF; idx += 128) {
@@ -1502,10 +1548,10 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         // issue queue is short, so the tensor cores would idle through that work; with two issuers one is always
         // queued up.  The only order the two must keep is on an S / dP buffer: tile t + 2 overwrites what the
         // accumulating MMAs of tile t read (buf_free, completed by the tensor cores themselves).
-        reg_dealloc<48>();
+        reg_dealloc<SA_R2_REST>();
         {
             const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
-            uint32_t nbf[2] = {0, 0}, g_base = 0, n_units = 0;
+            uint32_t g_base = 0, n_units = 0;
             const uint32_t idesc_full = make_idesc(128, kStreamRows, false, false, F16);
             const uint32_t a_s = smem_base + L::kStat0, c_s = smem_base + L::kStat1;
             for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
@@ -1518,18 +1564,17 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                     tc_fence_after();
                     for (int t = 0; t < ru.nt; ++t) {
                         const uint32_t g = g_base + t;
-                        const int stage = (int)(g % NS), b = t & 1;
+                        const int stage = (int)(g % NS), b = g & 1;
                         const int width = (t == ru.nt - 1) ? ru.last_width : kStreamRows;
                         const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
                         mbar_wait(&B.st_full[stage], (g / NS) & 1, wctx, 33);
-                        // the accumulating MMAs of the tile that used this buffer before have read its P and dS
-                        if (nbf[b] > 0) mbar_wait(&buf_free[b], (nbf[b] - 1) & 1, wctx, 39);
+                        // the accumulating MMAs of the tile that used this buffer before (two tiles back) have read its P and dS
+                        if (g >= 2) mbar_wait(&buf_free[b], ((g >> 1) - 1) & 1, wctx, 39);
                         SA_TR(0, 3);
                         tc_fence_after();
                         issue_sdp<HD>(leader, tm_s[b], tm_dp[b], a_s, c_s, k1_t, v1_t, width == kStreamRows ? idesc_full : make_idesc(128, width, false, false, F16));
                         tc_commit(leader, &B.sdp_ready[b]);
                         if (t == ru.nt - 1) tc_commit(leader, B.stat_empty);     // A and C may be overwritten
-                        ++nbf[b];
                         SA_TR(0, 4);
                     }
                     g_base += ru.nt;
@@ -1539,22 +1584,21 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         __syncwarp();
     } else if (warp == 17) {
         // ---------------------------------------------------------------- MMA issuer of the accumulating U and G
-        reg_dealloc<48>();
+        reg_dealloc<SA_R2_REST>();
         {
             const uint32_t leader = elect_one();
-            uint32_t nb[2] = {0, 0}, g_base = 0, n_units = 0;
+            uint32_t g_base = 0, n_units = 0;
             for (long it = blockIdx.x; it < P.num_row_items; it += gridDim.x) {
                 const RowItem ri = row_item(P, it);
                 for (int i0 = ri.i_run0; i0 < ri.i_run1; i0 += QPT, ++n_units) {
                     const RowUnit ru = row_unit(P, i0);
                     for (int tp = 0; tp < ru.nt; ++tp) {
                         const uint32_t g = g_base + tp;
-                        const int stage = (int)(g % NS), b = tp & 1;
+                        const int stage = (int)(g % NS), b = g & 1;
                         const int width = (tp == ru.nt - 1) ? ru.last_width : kStreamRows;
                         const uint32_t k1_t = smem_base + L::kStream + stage * 2 * L::kSmallTile, v1_t = k1_t + L::kSmallTile;
-                        mbar_wait(&B.pds_ready[b], nb[b] & 1, wctx, 34);
+                        mbar_wait(&B.pds_ready[b], (g >> 1) & 1, wctx, 34);
                         SA_TR(5, 5);
-                        ++nb[b];
                         // the previous unit's U and G have been read out by the epilogue groups
                         if (tp == 0 && n_units > 0) { mbar_wait(B.acc_free, (n_units - 1) & 1, wctx, 38); SA_TR(5, 6); }
                         tc_fence_after();
@@ -1571,7 +1615,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         }
     } else if (warp == 18) {
         // ---------------------------------------------------------------- TMA: streamed K1 / V1 tiles
-        reg_dealloc<48>();
+        reg_dealloc<SA_R2_REST>();
         if (lane == 0) {
             prefetch_tensormap(&map_k1);
             prefetch_tensormap(&map_v1);
@@ -1598,7 +1642,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
         }
         __syncwarp();
     } else {
-        reg_dealloc<48>();
+        reg_dealloc<SA_R2_REST>();
     }
     tc_fence_before();
     __syncthreads();
