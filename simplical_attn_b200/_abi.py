@@ -51,7 +51,7 @@ def load():
         return _lib
     path = _build.LIB
     if _build.have_compiler():
-        path = _build.build()              # returns at once unless a source is newer than the library
+        path = _build.build()              # returns at once unless the library was built from other sources
     elif not os.path.exists(path):
         raise OSError(f"{path} is missing and there is no nvcc to build it")
     lib = ctypes.CDLL(path)

@@ -4,6 +4,7 @@
 """
 from __future__ import annotations
 
+import hashlib
 import os
 import subprocess
 import sys
@@ -31,27 +32,48 @@ def sources():
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cu"))
 
 
-def _stale() -> bool:
-    if not os.path.exists(LIB):
-        return True
-    t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
+STAMP = LIB + ".sources"      # digest of the sources the library was built from
+
+
+def _deps():
+    deps = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC))
     deps.append(os.path.join(os.path.dirname(PKG), "include", "simplicial_attn_b200.h"))
-    return any(os.path.getmtime(d) > t for d in deps)
+    return deps
+
+
+def source_digest() -> str:
+    """Digest of every file the library is compiled from and of the compiler flags.  File times are not
+    used: a copy of the tree (a checkout, an archive) need not preserve them."""
+    h = hashlib.sha256(" ".join(NVCC_FLAGS).encode())
+    for d in _deps():
+        h.update(os.path.basename(d).encode())
+        with open(d, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def _stale() -> bool:
+    if not os.path.exists(LIB) or not os.path.exists(STAMP):
+        return True
+    with open(STAMP) as f:
+        return f.read().strip() != source_digest()
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile the library if it is missing or older than its sources; returns its path."""
+    """Compile the library if it is missing or was built from other sources; returns its path."""
     if not force and not _stale():
         return LIB
     nvcc = nvcc_path()
     os.makedirs(LIB_DIR, exist_ok=True)
+    digest = source_digest()
     cmd = [nvcc] + NVCC_FLAGS + ["-o", LIB] + sources()
     res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed building " + LIB)
+    with open(STAMP, "w") as f:
+        f.write(digest + "\n")
     return LIB
 
 

@@ -13,15 +13,17 @@
 //
 // A block works on "units" of 2 row tiles (2 x 128 virtual rows = 2 * 128/DW consecutive queries,
 // DW = w2 rounded up to a power of two).  Both row tiles stream through the same K1/V1 column
-// tiles (128 K1 rows each; the last tile of a unit is only as wide as needed, in steps of 16).
+// tiles (64 K1 rows each, a four-stage TMA ring; the last tile of a unit is only as wide as needed,
+// in steps of 16).
 //
 // Warps: 0-3 softmax group of row tile 0, 4-7 the same for row tile 1; 8-11 the auxiliary group,
 // which forms the A tiles of the NEXT unit while the current one is in its last column tiles and
 // merges / writes the results of the unit that just finished, so that neither operand formation nor
 // the epilogue ever stops the tensor cores; warps 12 and 13 issue the MMAs of row tile 0 and 1 (two
 // issuers: the row tiles are independent streams, neither waits behind the other's barriers); warp
-// 14 issues the TMA loads.  Tensor memory: S0 | S1 (128 fp32 columns each, P overwrites S in place
-// as packed bf16) | T0 | T1 (D columns each).
+// 14 issues the TMA loads.  Tensor memory: two 64-column S buffers per row tile (S of the next tile
+// is computed while the softmax works on the current one; P overwrites S in place as packed 16-bit
+// values) | T0 | T1 (D columns each).
 #pragma once
 
 #include <type_traits>
@@ -33,6 +35,12 @@
 // warps are short of issue slots, not of special-function throughput -- so the default is 0.
 #ifndef SA_FWD_POLY_OF_8
 #define SA_FWD_POLY_OF_8 0
+#endif
+// Registers per thread of the softmax groups, the auxiliary group and the MMA / TMA warps (multiples of 8).
+#ifndef SA_FWD_REGS_SM
+#define SA_FWD_REGS_SM 152
+#define SA_FWD_REGS_AUX 144
+#define SA_FWD_REGS_REST 64
 #endif
 
 namespace sa {
@@ -205,13 +213,13 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
         if (lane == 0) mbar_arrive(bar);
     };
 
-    // Register pool of the block: what it was launched with, 512 x 128 = 2 x 128 x 152 (softmax groups) + 128 x 144
-    // (auxiliary group) + 128 x 64 (MMA / TMA warps).  Registers the launch left unused on the multiprocessor do NOT
+    // Register pool of the block: what it was launched with, 512 x 128 >= 128 x (2 x softmax groups + auxiliary group
+    // + MMA / TMA warps), at the register counts above.  Registers the launch left unused on the multiprocessor do NOT
     // belong to the block: an increase beyond the block's own pool never returns.
-    static_assert(2 * 128 * 152 + 128 * 144 + 128 * 64 <= kFwdThreads * 128, "register pool of the block");
+    static_assert(2 * 128 * SA_FWD_REGS_SM + 128 * SA_FWD_REGS_AUX + 128 * SA_FWD_REGS_REST <= kFwdThreads * 128, "register pool of the block");
     if (warp == 14) {
         // ------------------------------------------------------------------ TMA producer
-        reg_dealloc<64>();
+        reg_dealloc<SA_FWD_REGS_REST>();
         if (lane == 0) {
             prefetch_tensormap(&map_k1);
             prefetch_tensormap(&map_v1);
@@ -240,7 +248,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
         __syncwarp();
     } else if (warp == 12 || warp == 13) {
         // ------------------------------------------------------------------ MMA issuer of row tile r
-        reg_dealloc<64>();
+        reg_dealloc<SA_FWD_REGS_REST>();
         {
             const int r = warp - 12;
             const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
@@ -320,11 +328,11 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
         }
         __syncwarp();
     } else if (warp == 15) {
-        reg_dealloc<64>();
+        reg_dealloc<SA_FWD_REGS_REST>();
     } else if (warp >= 8) {
         // ------------------------------------------------------------------ auxiliary group: operand formation ahead of the
         // softmax groups, merge over delta and output behind them
-        reg_alloc<144>();
+        reg_alloc<SA_FWD_REGS_AUX>();
         const int row = tid & 127;                   // virtual row = tensor-memory lane
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
         const int qq = row >> P.dw_log2;
@@ -538,7 +546,7 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
         }
     } else {
         // ------------------------------------------------------------------ softmax groups
-        reg_alloc<152>();
+        reg_alloc<SA_FWD_REGS_SM>();
         const int r = warp >> 2;                     // row tile of this group
         const int row = tid & 127;                   // virtual row = tensor-memory lane
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
