@@ -262,6 +262,14 @@ struct ColSmem {
 // shared memory either way) and in long bursts.  S^T / dP^T are not double buffered (tensor memory
 // is full: 128 + 128 + 2 x 128 accumulator columns); instead both softmax groups work on the same
 // tile, group g on columns [64g, 64g + 64), and write P / dS back inside their own column range.
+// Registers per thread of the column kernel's softmax groups, producers and remaining warps (multiples of 8).
+#ifndef SA_COL_SM
+#define SA_COL_SM 96
+#define SA_COL_PR 112
+#define SA_COL_REST 64
+#endif
+static_assert(128 * (2 * SA_COL_SM + 2 * SA_COL_PR + SA_COL_REST) <= 640 * 96 && SA_COL_SM >= 96 && SA_COL_PR >= 96,
+              "register pool of the column kernel's block");
 template <int HD, bool BIAS, bool F16 = false>
 __global__ void __launch_bounds__(kColThreads, 1)
 bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CUtensorMap map_k1,
@@ -321,8 +329,9 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
 
     if (warp < 8) {
         // ---------------------------------------------------------------- softmax groups + epilogue
-        // Register pool of the block: 640 x 96 = 2 x 96 (softmax groups, unchanged) + 2 x 112 (producers) + 64
-        // (MMA / TMA group): an increase beyond the block's own pool would never return.
+        // Register pool of the block: 640 x 96 = 128 x (2 x softmax groups + 2 x producers + MMA / TMA group) at the
+        // counts SA_COL_*: an increase beyond the block's own pool would never return.
+        reg_alloc<SA_COL_SM>();
         const int grp = warp >> 2;
         const int row = tid & 127;                       // tensor-memory lane = K1/V1 row of the block's tile
         const uint32_t lane_addr = ((uint32_t)(row & ~31)) << 16;
@@ -448,7 +457,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         }
     } else if (warp < 16) {
         // ---------------------------------------------------------------- producers: group 0 forms A, group 1 forms C
-        reg_alloc<112>();
+        reg_alloc<SA_COL_PR>();
         const int grp = (warp - 8) >> 2;
         const int row = tid & 127;
         // DWL: compile-time log2 of the delta slots per query for 16, 32 and 64 slots (the operand rows of a tile are
@@ -533,7 +542,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         }
     } else if (warp == 16) {
         // ---------------------------------------------------------------- MMA issuer
-        reg_dealloc<64>();
+        reg_dealloc<SA_COL_REST>();
         {
             const uint32_t leader = elect_one();      // the whole warp runs the loop; one lane issues
             uint32_t g_base = 0, n_items = 0;
@@ -604,7 +613,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         __syncwarp();
     } else if (warp == 17) {
         // ---------------------------------------------------------------- TMA: the block's K1 / V1 rows
-        reg_dealloc<64>();
+        reg_dealloc<SA_COL_REST>();
         if (lane == 0) {
             prefetch_tensormap(&map_k1);
             prefetch_tensormap(&map_v1);
@@ -624,7 +633,7 @@ bwd_col_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
         }
         __syncwarp();
     } else {
-        reg_dealloc<64>();
+        reg_dealloc<SA_COL_REST>();
     }
     tc_fence_before();
     __syncthreads();
@@ -1141,13 +1150,17 @@ constexpr int row2_stage_bytes(int dwl, int hd) {
     return dwl > 5 ? 0 : 2 * (128 >> dwl) * hd * 2 + ((1 << dwl) + (128 >> dwl) - 1) * (hd * 2 + 16);
 }
 
+// Registers per thread of the softmax groups, the operand / epilogue groups and the remaining warps of the row
+// kernel below (multiples of 8; 128 x (2 SM + 2 EP + REST) must not exceed the block's launch allocation, 640 x 96).
+// Measured: the operand / epilogue groups are the ones that need them (their unit of work holds 64 registers of
+// accumulator data): 96 / 128 / 32 is 10 % faster at short windows than 104 / 112 / 48 and equal at long ones.
 #ifndef SA_R2_SM
-#define SA_R2_SM 104
-#define SA_R2_EP 112
+#define SA_R2_SM 96
+#define SA_R2_EP 128
+#define SA_R2_REST 32
 #endif
-#ifndef SA_R2_REST
-#define SA_R2_REST 48
-#endif
+static_assert(128 * (2 * SA_R2_SM + 2 * SA_R2_EP + SA_R2_REST) <= 640 * 96 && SA_R2_SM >= 96 && SA_R2_EP >= 96,
+              "register pool of the row kernel's block; an increase must not go below the launch allocation");
 constexpr int kRow2Threads = 640;     // softmax groups (0-7), epilogue groups (8-15), MMA issuers (16, 17), TMA (18), 1 idle
 
 template <int HD, int DWL, int NS, bool BIAS, bool F16 = false>
@@ -1218,8 +1231,8 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
     const uint32_t tm_dp[2] = {tmem_base + 128, tmem_base + 192};
     const uint32_t tm_u = tmem_base + 256, tm_g = tmem_base + 384;     // U = P V1, G = dS K1
 
-    // Register pool of the block: 640 x 96 = 128 x (2 x 104 (softmax groups) + 2 x 112 (operand / epilogue groups) +
-    // 48 (the rest)): an increase beyond the block's own pool would never return.
+    // Register pool of the block: 640 x 96 = 128 x (2 x softmax groups + 2 x operand / epilogue groups + the rest) at
+    // the counts SA_R2_*: an increase beyond the block's own pool would never return.
     if (warp < 8) {
         // ---------------------------------------------------------------- softmax
         // Every column tile (64 columns) is split between the two groups: group g turns columns [32g, 32g + 32)
