@@ -42,7 +42,9 @@ typedef enum {
 typedef enum { SA_BF16 = 0, SA_F16 = 1, SA_F32 = 2 } sa_dtype;
 
 /* Kernel family.  AUTO picks the tcgen05 kernels whenever they cover the problem (bf16 or fp16, D in
- * {64,128}, effective w2 <= 128) and the general kernels otherwise.  The general kernels are plain
+ * {64,128}, effective w2 <= 1024; a K2 window wider than 128 positions is processed in passes over
+ * 128-position chunks whose results are merged, with temporaries in the workspace) and the general
+ * kernels otherwise.  The general kernels are plain
  * CUDA-core fp32 code for every dtype, head dim and window; they also serve as the on-device
  * cross-check of the tensor-core kernels. */
 typedef enum { SA_ALGO_AUTO = 0, SA_ALGO_GENERAL = 1, SA_ALGO_TCGEN05 = 2 } sa_algo;
@@ -108,7 +110,8 @@ int sa_read_status_static(void* stream);
 
 /* Workspace sizes in bytes for the given problem (the reference allocates its work buffers inside
  * the autograd function, triton_impl.py:23-25,73-77; here the caller does).  Never 0: the first
- * 256 bytes hold the device status word. */
+ * 256 bytes hold the device status word.  The sizes depend on the windows (a K2 window wider than
+ * 128 positions needs room for one more O / LSE, or one more set of gradients). */
 size_t sa_forward_workspace_size(const sa_params* p);
 size_t sa_backward_workspace_size(const sa_params* p);
 

@@ -27,6 +27,9 @@ std::atomic<uint64_t> g_wait_limit_ns{sa::ptx::kWaitLimitNs};   // bound of ever
 constexpr size_t kStaticScratchBytes = 32u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
+constexpr int kChunkW2 = 128;      // K2 positions one pass of the tensor-core kernels covers
+constexpr int kMaxChunks = 8;      // passes the library is willing to chain (wider windows: general kernels)
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 bool stride_ok8(const sa_strides& s) { return s.b % 8 == 0 && s.n % 8 == 0 && s.h % 8 == 0; }
 
@@ -61,7 +64,7 @@ bool tc_shape_ok(const sa_params* p, bool backward) {
     const KParams k = make_kparams(p);
     if (p->dtype != SA_BF16 && p->dtype != SA_F16) return false;
     if (p->D != 64 && p->D != 128) return false;
-    if (k.w2 > 128) return false;
+    if (k.w2 > kChunkW2 * kMaxChunks) return false;
     if (p->scale <= 0.f) return false;            // the row maximum is taken before scaling
     if (!stride_ok8(p->q) || !stride_ok8(p->k1) || !stride_ok8(p->k2) || !stride_ok8(p->v1) || !stride_ok8(p->v2) ||
         !stride_ok8(p->o))
@@ -125,6 +128,106 @@ __global__ void __launch_bounds__(32) wait_timeout_probe_kernel(sa::DeviceStatus
     const sa::ptx::WaitCtx ctx{&abort_flag, status, limit_ns};
     sa::ptx::mbar_wait(&bar, 0, ctx, where);      // phase 0 never completes
     sa::ptx::mbar_wait(&bar, 0, ctx, where + 1);  // after the first wait gave up every later wait falls through
+}
+
+// ---- K2 windows wider than one pass of the tensor-core kernels (128 positions).  The window is cut into chunks of
+// at most 128 positions; chunk c is an ordinary call whose K2/V2 rows sit 128 c rows further back, which is what a
+// halo of halo2 - 128 c rows means (rows before the buffer's start do not exist and are masked as always).  Forward:
+// the chunks' outputs are merged by their log-sum-exp.  Backward: with the merged O and LSE every chunk's
+// probabilities are already normalised over the whole window, so the chunks' gradients simply add.
+int num_chunks(const KParams& k) { return (k.w2 + kChunkW2 - 1) / kChunkW2; }
+
+KParams chunk_params(const KParams& k, int c) {
+    KParams kc = k;
+    kc.halo2 = k.halo2 - c * kChunkW2;
+    kc.n2 = k.N + kc.halo2;
+    kc.w2 = k.w2 - c * kChunkW2 < kChunkW2 ? k.w2 - c * kChunkW2 : kChunkW2;
+    return kc;
+}
+
+size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+sa_strides contiguous_strides(int rows, int heads, int D) {
+    return sa_strides{(int64_t)rows * heads * D, (int64_t)heads * D, (int64_t)D};
+}
+
+// Temporaries of the chunked calls, behind the status word (and, in the backward, the kernels' own workspace).
+struct ChunkTemps {
+    size_t o, lse, dq, dk1, dv1, dk2, dv2, total;
+};
+ChunkTemps chunk_temps(const KParams& k, bool backward) {
+    ChunkTemps t{};
+    size_t off = 0;
+    auto take = [&](size_t bytes) { const size_t at = off; off += align256(bytes); return at; };
+    if (!backward) {
+        t.o = take((size_t)k.B * k.N * k.H * k.D * 2);
+        t.lse = take((size_t)k.B * k.H * k.N * 4);
+    } else {
+        t.dq = take((size_t)k.B * k.N * k.H * k.D * 2);
+        t.dk1 = take((size_t)k.B * k.n1 * k.Hkv * k.D * 2);
+        t.dv1 = take((size_t)k.B * k.n1 * k.Hkv * k.D * 2);
+        t.dk2 = take((size_t)k.B * k.n2 * k.Hkv * k.D * 2);
+        t.dv2 = take((size_t)k.B * k.n2 * k.Hkv * k.D * 2);
+    }
+    t.total = off;
+    return t;
+}
+
+// o = (e^lse o + e^lse_t o_t) / (e^lse + e^lse_t), eight elements per thread; lse is updated afterwards by
+// merge_lse_kernel (every thread of a row reads the old value here).
+template <typename T>
+__global__ void __launch_bounds__(256) merge_o_kernel(T* __restrict__ o, sa_strides so, const float* __restrict__ lse,
+                                                      const T* __restrict__ o_t, const float* __restrict__ lse_t, int B, int N,
+                                                      int H, int D) {
+    const int cpr = D / 8;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)B * N * H * cpr) return;
+    const int c = (int)(idx % cpr), h = (int)((idx / cpr) % H), n = (int)((idx / cpr / H) % N), b = (int)(idx / cpr / H / N);
+    const long li = ((long)b * H + h) * N + n;
+    const float l0 = lse[li], l1 = lse_t[li];
+    if (!(l1 > -INFINITY)) return;                     // this chunk holds nothing for the query
+    const float m = fmaxf(l0, l1);
+    const float w0 = __expf(l0 - m), w1 = __expf(l1 - m), inv = 1.f / (w0 + w1);
+    T* dst = o + b * so.b + (long)n * so.n + h * so.h + c * 8;
+    const T* src = o_t + (((long)b * N + n) * H + h) * D + c * 8;
+    uint4 a = *reinterpret_cast<const uint4*>(dst), t = *reinterpret_cast<const uint4*>(src);
+    T* av = reinterpret_cast<T*>(&a);
+    const T* tv = reinterpret_cast<const T*>(&t);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) av[e] = sa::from_f<T>((w0 * sa::to_f<T>(av[e]) + w1 * sa::to_f<T>(tv[e])) * inv);
+    *reinterpret_cast<uint4*>(dst) = a;
+}
+
+__global__ void __launch_bounds__(256) merge_lse_kernel(float* __restrict__ lse, const float* __restrict__ lse_t, long n) {
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= n) return;
+    const float l0 = lse[idx], l1 = lse_t[idx];
+    if (!(l1 > -INFINITY)) return;
+    const float m = fmaxf(l0, l1);
+    lse[idx] = m + __logf(__expf(l0 - m) + __expf(l1 - m));
+}
+
+// dst[b, r, h, :] += tmp[b, r, h, :] for r < rows (tmp contiguous [B, rows, heads, D]), eight elements per thread
+template <typename T>
+__global__ void __launch_bounds__(256) add_rows_kernel(T* __restrict__ dst, sa_strides sd, const T* __restrict__ tmp, int B,
+                                                       int rows, int heads, int D) {
+    const int cpr = D / 8;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long)B * rows * heads * cpr) return;
+    const int c = (int)(idx % cpr), h = (int)((idx / cpr) % heads), r = (int)((idx / cpr / heads) % rows),
+              b = (int)(idx / cpr / heads / rows);
+    T* d = dst + b * sd.b + (long)r * sd.n + h * sd.h + c * 8;
+    uint4 a = *reinterpret_cast<const uint4*>(d), t = *reinterpret_cast<const uint4*>(tmp + idx * 8);
+    T* av = reinterpret_cast<T*>(&a);
+    const T* tv = reinterpret_cast<const T*>(&t);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) av[e] = sa::from_f<T>(sa::to_f<T>(av[e]) + sa::to_f<T>(tv[e]));
+    *reinterpret_cast<uint4*>(d) = a;
+}
+
+template <typename T>
+void launch_add_rows(void* dst, const sa_strides& sd, const void* tmp, int B, int rows, int heads, int D, cudaStream_t st) {
+    const long total = (long)B * rows * heads * (D / 8);
+    add_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((T*)dst, sd, (const T*)tmp, B, rows, heads, D);
 }
 
 struct DeviceInfo {
@@ -212,10 +315,92 @@ int launch_fwd_tc_t(const KParams& k, const void* q, const void* k1, const void*
     return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
 }
 
-int launch_fwd_tc(const sa_params* p, const KParams& k, const void* q, const void* k1, const void* k2, const void* v1,
-                  const void* v2, void* o, float* lse, void* workspace, cudaStream_t st) {
+int launch_fwd_tc_one(const sa_params* p, const KParams& k, const void* q, const void* k1, const void* k2, const void* v1,
+                      const void* v2, void* o, float* lse, void* workspace, cudaStream_t st) {
     return p->dtype == SA_F16 ? launch_fwd_tc_t<true>(k, q, k1, k2, v1, v2, o, lse, workspace, st)
                               : launch_fwd_tc_t<false>(k, q, k1, k2, v1, v2, o, lse, workspace, st);
+}
+
+// One pass, or one pass per 128-position chunk of the K2 window merged into o / lse.
+int launch_fwd_tc(const sa_params* p, const KParams& k, const void* q, const void* k1, const void* k2, const void* v1,
+                  const void* v2, void* o, float* lse, void* workspace, cudaStream_t st) {
+    const int nc = num_chunks(k);
+    if (nc == 1) return launch_fwd_tc_one(p, k, q, k1, k2, v1, v2, o, lse, workspace, st);
+    const ChunkTemps t = chunk_temps(k, false);
+    uint8_t* base = static_cast<uint8_t*>(workspace) + kStatusBytes;
+    void* o_t = base + t.o;
+    float* lse_t = reinterpret_cast<float*>(base + t.lse);
+    for (int c = 0; c < nc; ++c) {
+        KParams kc = chunk_params(k, c);
+        if (c > 0) kc.o = contiguous_strides(k.N, k.H, k.D);
+        const int rc = launch_fwd_tc_one(p, kc, q, k1, k2, v1, v2, c == 0 ? o : o_t, c == 0 ? lse : lse_t, workspace, st);
+        if (rc != SA_OK) return rc;
+        if (c == 0) continue;
+        const long total = (long)k.B * k.N * k.H * (k.D / 8);
+        if (p->dtype == SA_F16)
+            merge_o_kernel<__half><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((__half*)o, k.o, lse, (const __half*)o_t, lse_t,
+                                                                                      k.B, k.N, k.H, k.D);
+        else
+            merge_o_kernel<__nv_bfloat16><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+                (__nv_bfloat16*)o, k.o, lse, (const __nv_bfloat16*)o_t, lse_t, k.B, k.N, k.H, k.D);
+        const long rows = (long)k.B * k.H * k.N;
+        merge_lse_kernel<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(lse, lse_t, rows);
+        g_launches += 2;
+    }
+    return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
+}
+
+// Workspace of the tensor-core backward: the kernels' own (the largest over the chunks) and, with more than one
+// chunk, the temporaries the later chunks' gradients are written to before they are added.
+size_t bwd_tc_kernel_workspace(const KParams& k) {
+    size_t m = 0;
+    for (int c = 0; c < num_chunks(k); ++c) {
+        const size_t b = sa::tc::bwd_workspace_bytes(chunk_params(k, c), plan_sm_count());
+        m = b > m ? b : m;
+    }
+    return align256(m);
+}
+
+// Returns an sa_status, or -1 when the tensor-core backward declines the problem (nothing has been launched then).
+int launch_bwd_tc(const sa_params* p, const KParams& k, const void* q, const void* k1, const void* k2, const void* v1,
+                  const void* v2, const void* o, const float* lse, const void* d_o, void* dq, void* dk1, void* dk2, void* dv1,
+                  void* dv2, void* workspace, cudaStream_t st) {
+    const int nc = num_chunks(k);
+    uint8_t* kernel_ws = static_cast<uint8_t*>(workspace) + kStatusBytes;
+    sa::DeviceStatus* status = reinterpret_cast<sa::DeviceStatus*>(workspace);
+    const bool f16 = p->dtype == SA_F16;
+    const ChunkTemps t = chunk_temps(k, true);
+    uint8_t* temps = kernel_ws + bwd_tc_kernel_workspace(k);
+    for (int c = 0; c < nc; ++c) {
+        KParams kc = chunk_params(k, c);
+        void *cq = dq, *ck1 = dk1, *ck2 = dk2, *cv1 = dv1, *cv2 = dv2;
+        if (c > 0) {
+            if (dq) { cq = temps + t.dq; kc.dq = contiguous_strides(k.N, k.H, k.D); }
+            if (dk1) { ck1 = temps + t.dk1; kc.dk1 = contiguous_strides(k.n1, k.Hkv, k.D); }
+            if (dv1) { cv1 = temps + t.dv1; kc.dv1 = contiguous_strides(k.n1, k.Hkv, k.D); }
+            if (dk2) { ck2 = temps + t.dk2; kc.dk2 = contiguous_strides(kc.n2, k.Hkv, k.D); }
+            if (dv2) { cv2 = temps + t.dv2; kc.dv2 = contiguous_strides(kc.n2, k.Hkv, k.D); }
+        }
+        int nlaunch = 0;
+        const int rc = sa::tc::launch_bwd(kc, q, k1, k2, v1, v2, o, lse, d_o, cq, ck1, ck2, cv1, cv2, kernel_ws, status, st, &nlaunch,
+                                          &make_map, plan_sm_count(), g_wait_limit_ns.load(), f16);
+        g_launches += nlaunch;
+        if (rc == -1) return c == 0 ? -1 : SA_ERR_UNSUPPORTED;
+        if (rc != SA_OK) return rc;
+        if (c == 0) continue;
+        auto add = [&](void* dst, const sa_strides& sd, void* tmp, int rows, int heads) {
+            if (!dst) return;
+            if (f16) launch_add_rows<__half>(dst, sd, tmp, k.B, rows, heads, k.D, st);
+            else launch_add_rows<__nv_bfloat16>(dst, sd, tmp, k.B, rows, heads, k.D, st);
+            g_launches += 1;
+        };
+        add(dq, k.dq, cq, k.N, k.H);
+        add(dk1, k.dk1, ck1, k.n1, k.Hkv);
+        add(dv1, k.dv1, cv1, k.n1, k.Hkv);
+        add(dk2, k.dk2, ck2, kc.n2, k.Hkv);      // a later chunk reaches only the first n2 - 128 c rows
+        add(dv2, k.dv2, cv2, kc.n2, k.Hkv);
+    }
+    return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
 }
 
 int resolve(const sa_params* p, bool backward) {
@@ -279,14 +464,16 @@ int sa_resolve_algo(const sa_params* p) {
 }
 
 size_t sa_forward_workspace_size(const sa_params* p) {
-    (void)p;
-    return kStatusBytes;
+    if (validate(p) != SA_OK || resolve(p, false) != SA_ALGO_TCGEN05) return kStatusBytes;
+    const KParams k = make_kparams(p);
+    return kStatusBytes + (num_chunks(k) > 1 ? chunk_temps(k, false).total : 0);
 }
 
 size_t sa_backward_workspace_size(const sa_params* p) {
     if (validate(p) != SA_OK) return kStatusBytes;
     if (resolve(p, true) != SA_ALGO_TCGEN05) return kStatusBytes;
-    return kStatusBytes + sa::tc::bwd_workspace_bytes(make_kparams(p), plan_sm_count());
+    const KParams k = make_kparams(p);
+    return kStatusBytes + bwd_tc_kernel_workspace(k) + (num_chunks(k) > 1 ? chunk_temps(k, true).total : 0);
 }
 
 int sa_read_status_ex(void* workspace, void* stream, int* where, int* block) {
@@ -365,12 +552,7 @@ int sa_backward(const sa_params* p, const void* q, const void* k1, const void* k
     }
     if (algo == SA_ALGO_TCGEN05) {
         if (device_info().cc_major != 10) return SA_ERR_NOT_SM100;
-        int nlaunch = 0;
-        const int rc = sa::tc::launch_bwd(k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2,
-                                          static_cast<uint8_t*>(workspace) + kStatusBytes,
-                                          reinterpret_cast<sa::DeviceStatus*>(workspace), st, &nlaunch, &make_map,
-                                          plan_sm_count(), g_wait_limit_ns.load(), p->dtype == SA_F16);
-        g_launches += nlaunch;
+        const int rc = launch_bwd_tc(p, k, q, k1, k2, v1, v2, o, lse, d_o, dq, dk1, dk2, dv1, dv2, workspace, st);
         if (rc != -1) return rc;      // -1: the tensor-core backward declines this problem
         if (p->algo == SA_ALGO_TCGEN05) return SA_ERR_UNSUPPORTED;
     }

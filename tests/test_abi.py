@@ -66,14 +66,21 @@ def test_kernel_selection():
     assert r(D=32) == _abi.SA_ALGO_GENERAL
     assert r(dtype=_abi.SA_F32) == _abi.SA_ALGO_GENERAL
     assert r(dtype=_abi.SA_F16) == _abi.SA_ALGO_TCGEN05
-    assert r(w2=200, N=4096) == _abi.SA_ALGO_GENERAL
+    assert r(w2=200, N=4096) == _abi.SA_ALGO_TCGEN05                         # two passes over chunks of the K2 window
+    assert r(w2=1025, N=4096) == _abi.SA_ALGO_GENERAL
     assert r(w2=200, N=64) == _abi.SA_ALGO_TCGEN05                           # window clipped to 64 rows
     assert r(algo=_abi.SA_ALGO_GENERAL) == _abi.SA_ALGO_GENERAL
     assert r(D=32, algo=_abi.SA_ALGO_TCGEN05) == -4
     assert r(q=_abi.Strides(1000, 100, 4)) == _abi.SA_ALGO_GENERAL           # rows not 16-byte aligned
     assert r(H=5) == -2
-    assert lib.sa_forward_workspace_size(ctypes.byref(_params())) >= 256
+    assert lib.sa_forward_workspace_size(ctypes.byref(_params())) == 256
     assert lib.sa_backward_workspace_size(ctypes.byref(_params())) >= 256
+    # a K2 window of more than 128 positions: room for one more O (bf16) and LSE (fp32) in the forward, for one
+    # more set of gradients in the backward
+    wide, narrow = _params(w2=200, N=4096), _params(w2=100, N=4096)
+    assert lib.sa_forward_workspace_size(ctypes.byref(wide)) == 256 + 4096 * 4 * 128 * 2 + 4 * 4096 * 4
+    extra = lib.sa_backward_workspace_size(ctypes.byref(wide)) - lib.sa_backward_workspace_size(ctypes.byref(narrow))
+    assert extra >= (4096 * 4 * 128 + 4 * 4096 * 2 * 128) * 2
 
 
 def test_python_layer_rejects_cpu_tensors():

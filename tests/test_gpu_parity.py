@@ -46,7 +46,7 @@ def _run(ins, cfg, algo, dtype=torch.bfloat16, need=(True,) * 5, halo1=0, halo2=
 
 
 def _tc_supported(cfg):
-    return cfg["D"] in (64, 128) and min(cfg["w2"], cfg["N"]) <= 128
+    return cfg["D"] in (64, 128) and min(cfg["w2"], cfg["N"]) <= 1024
 
 
 @pytest.mark.parametrize("name", gu.names())
@@ -100,6 +100,34 @@ def test_vs_cpu_oracle(case, algo):
     cfg = dict(w1=w1, w2=w2, scale=scale, k2_bias=kb, v2_bias=vb)
     ins = dict(q=q, k1=k1, k2=k2, v1=v1, v2=v2, do=do)
     o, lse, grads = _run(ins, cfg, algo, halo1=h1, halo2=h2)
+    ref = so.forward_backward(q, k1, k2, v1, v2, do, w1, w2, scale, kb, vb, h1, h2)
+    assert float((o.float().cpu() - ref[0]).abs().max()) <= TOL_O_BF16
+    assert float((lse.cpu() - ref[1]).abs().max()) <= 2e-2
+    for nm, g, r in zip(("dq", "dk1", "dk2", "dv1", "dv2"), grads, ref[2:]):
+        assert _grad_err(g, r) <= TOL_G_BF16, nm
+
+
+# K2 windows wider than one pass of the tensor-core kernels (128 positions): the library chains passes over
+# 128-position chunks of the window.  B, N, H, Hkv, D, w1, w2, k2_bias, v2_bias, halo1, halo2
+WIDE_K2_CASES = [
+    (1, 400, 2, 1, 128, 64, 256, 0.0, 0.0, 0, 0),      # two full chunks, grouped heads
+    (1, 330, 2, 2, 128, 40, 160, 0.0, 0.0, 0, 0),      # a full chunk and a 32-position one
+    (1, 300, 1, 1, 64, 48, 300, 0.1, -0.1, 0, 0),      # window wider than the sequence is long, D = 64, biases, three chunks
+    (1, 200, 2, 2, 128, 30, 200, 0.0, 0.0, 29, 199),   # a sequence shard with halo rows in front
+]
+
+
+@pytest.mark.parametrize("case", WIDE_K2_CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+def test_wide_k2_window_vs_cpu_oracle(case, dtype):
+    B, N, H, Hkv, D, w1, w2, kb, vb, h1, h2 = case
+    q, k1, k2, v1, v2, do = so.make_inputs(B, N, H, Hkv, D, seed=5, seed_do=6, halo1=h1, halo2=h2)
+    scale = 1.0 / math.sqrt(D)
+    cfg = dict(w1=w1, w2=w2, scale=scale, k2_bias=kb, v2_bias=vb)
+    ins = dict(q=q, k1=k1, k2=k2, v1=v1, v2=v2, do=do)
+    o, lse, grads = _run(ins, cfg, "tcgen05", dtype=dtype, halo1=h1, halo2=h2)
+    if dtype == torch.float16:
+        q, k1, k2, v1, v2, do = (t.to(torch.float16).float() for t in (q, k1, k2, v1, v2, do))
     ref = so.forward_backward(q, k1, k2, v1, v2, do, w1, w2, scale, kb, vb, h1, h2)
     assert float((o.float().cpu() - ref[0]).abs().max()) <= TOL_O_BF16
     assert float((lse.cpu() - ref[1]).abs().max()) <= 2e-2
