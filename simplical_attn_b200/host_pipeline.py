@@ -16,14 +16,62 @@ strided (pieces of `heads * D` elements, `H * D` apart); it moves with one strid
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import math
+import os
 from typing import List, Optional, Sequence, Tuple
 
 import torch
 
 from . import _abi
 from . import simplicial_attn as _op
+
+
+def _cpu_list(text: str) -> set:
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def local_cpus(device) -> Optional[set]:
+    """CPUs on the NUMA node the GPU's PCIe slot hangs off (from sysfs), or None where the system does
+    not say (a container without that part of sysfs, a single-node host)."""
+    try:
+        pr = torch.cuda.get_device_properties(torch.device(device))
+        path = "/sys/bus/pci/devices/%04x:%02x:%02x.0/local_cpulist" % (pr.pci_domain_id, pr.pci_bus_id, pr.pci_device_id)
+        with open(path) as f:
+            cpus = _cpu_list(f.read())
+        return cpus or None
+    except (OSError, AttributeError, ValueError):
+        return None
+
+
+@contextlib.contextmanager
+def near(device):
+    """Host memory allocated inside this block (pinned buffers in particular) comes from the NUMA node of
+    the GPU: the calling thread is confined to that node's CPUs for the duration, and pages are placed
+    where the thread that first touches them runs.  With one process per GPU on a two-socket host this
+    keeps every process's transfers off the socket interconnect.  Does nothing where the node is unknown
+    or none of its CPUs is available to the process; yields whether it took effect."""
+    cpus = local_cpus(device)
+    try:
+        before = os.sched_getaffinity(0)
+    except (AttributeError, OSError):
+        before = None
+    use = (cpus & before) if (cpus and before) else None
+    if use and use != before:
+        os.sched_setaffinity(0, use)
+        try:
+            yield True
+        finally:
+            os.sched_setaffinity(0, before)
+    else:
+        yield False
 
 
 def plan_chunks(batch: int, kv_heads: int, edge_fraction: float = 0.25) -> List[Tuple[int, int, int]]:
