@@ -496,9 +496,9 @@ def main():
             "bwd_row_kernel": (ms_row, 3.0 * unit_rank, TRAFFIC["bwd_row_kernel"] * Bl),
         }
         # the row kernel has two variants; the library picks the one with separate operand / epilogue warpgroups for
-        # head dim 128 and 9..64 K2 positions per query (the bench workload)
+        # 9..64 K2 positions per query (the bench workload)
         symbols = {"fwd_tc_kernel": "fwd_tc_kernel", "bwd_col_kernel": "bwd_col_kernel",
-                   "bwd_row_kernel": "bwd_row2_kernel" if (cfg["D"] == 128 and 9 <= cfg["w2"] <= 64) else "bwd_row_kernel"}
+                   "bwd_row_kernel": "bwd_row2_kernel" if 9 <= cfg["w2"] <= 64 else "bwd_row_kernel"}
         dom = max(kernels, key=lambda k: kernels[k][0])
         dom_ms, dom_fl, dom_traffic = kernels[dom]
         achieved = dom_fl / (dom_ms * 1e-3) / 1e12

@@ -220,8 +220,14 @@ __device__ __forceinline__ void tc_commit(uint32_t leader, uint64_t* bar) {
         : "memory");
 }
 
-// Each lane of the warp reads 16 (32) consecutive 32-bit columns of its own tensor-memory lane
+// Each lane of the warp reads 8 (16, 32) consecutive 32-bit columns of its own tensor-memory lane
 // (lane = 32 * (warp % 4) + laneid, encoded in bits 16.. of `addr`).
+__device__ __forceinline__ void tmem_ld8(uint32_t addr, uint32_t (&v)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+                 : "r"(addr)
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t addr, uint32_t (&v)[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -590,17 +596,19 @@ __device__ __forceinline__ void form_query_tile(uint8_t* tile, int slab_bytes, i
     }
 }
 
-// Sum over the 32 lanes of a warp of CW values per lane; afterwards lane L holds the total of
-// value (L % CW) in v[0].  A halving exchange: each step a lane keeps one half of its values and
-// adds the partner's copy of that half, 31 shuffles for 32 values.
+// Sum over the 32 lanes of a warp of CW values per lane (CW = 8, 16 or 32); afterwards lane L holds the
+// total of value (L % CW) in v[0].  Lane bits at or above CW are summed plainly, the rest by a halving
+// exchange: each step a lane keeps one half of its values and adds the partner's copy of that half
+// (31 shuffles for 32 values).
 template <int CW>
 __device__ __forceinline__ float warp_transpose_reduce(float (&v)[CW], int lane) {
-    if constexpr (CW == 16) {
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] += __shfl_xor_sync(0xffffffffu, v[j], 16);
+    for (int m = 16; m >= CW; m >>= 1) {
+#pragma unroll
+        for (int j = 0; j < CW; ++j) v[j] += __shfl_xor_sync(0xffffffffu, v[j], m);
     }
 #pragma unroll
-    for (int s = (CW == 32 ? 16 : 8); s >= 1; s >>= 1) {
+    for (int s = (CW == 32 ? 16 : CW / 2); s >= 1; s >>= 1) {
         const bool upper = (lane & s) != 0;
 #pragma unroll
         for (int j = 0; j < s; ++j) {
@@ -612,12 +620,17 @@ __device__ __forceinline__ float warp_transpose_reduce(float (&v)[CW], int lane)
     return v[0];
 }
 
-
-// The same exchange within each half of the warp (lanes 0-15 and 16-31 separately), for 16 values:
-// lane L ends up with the total, over its 16-lane half, of value (L % 16).
-__device__ __forceinline__ float half_warp_transpose_reduce16(float (&v)[16], int lane) {
+// The same within each half of the warp (lanes 0-15 and 16-31 separately), for CW = 8 or 16 values:
+// lane L ends up with the total, over its 16-lane half, of value (L % CW).
+template <int CW>
+__device__ __forceinline__ float half_warp_transpose_reduce(float (&v)[CW], int lane) {
 #pragma unroll
-    for (int s = 8; s >= 1; s >>= 1) {
+    for (int m = 8; m >= CW; m >>= 1) {
+#pragma unroll
+        for (int j = 0; j < CW; ++j) v[j] += __shfl_xor_sync(0xffffffffu, v[j], m);
+    }
+#pragma unroll
+    for (int s = (CW == 16 ? 8 : CW / 2); s >= 1; s >>= 1) {
         const bool upper = (lane & s) != 0;
 #pragma unroll
         for (int j = 0; j < s; ++j) {
@@ -627,6 +640,9 @@ __device__ __forceinline__ float half_warp_transpose_reduce16(float (&v)[16], in
         }
     }
     return v[0];
+}
+__device__ __forceinline__ float half_warp_transpose_reduce16(float (&v)[16], int lane) {
+    return half_warp_transpose_reduce<16>(v, lane);
 }
 
 // Byte offset of element (row, col) inside a 128-byte-swizzled [rows x 64] bf16 slab.

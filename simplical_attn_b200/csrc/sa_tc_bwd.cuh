@@ -22,15 +22,16 @@
 //                       memory, merges G over delta into dQ and adds the per-K2-row sums of G*Q and
 //                       U*dO into fp32 partial buffers in the workspace (plain read-modify-write:
 //                       a row is only ever touched by one block, in program order).  The second
-//                       form has separate epilogue warpgroups (32 delta slots per query, D = 128).
+//                       form (16, 32 or 64 delta slots per query, D = 128) has separate warpgroups that
+//                       form the operands and run the epilogue, see there.
 //   4. kv2_reduce_kernel sums those partials over the query heads of a group and over run
 //                       boundaries and writes dK2, dV2.
 //
-// Row kernels: S and dP tiles (128 lanes x 64 columns) are double buffered in tensor memory; softmax
-// group b (4 warps) turns buffer b into P and dS (bf16, in place) while the tensor cores work on the
-// other buffer; P and dS then feed the two accumulating MMAs from tensor memory.  Column kernel: one
-// 128-column S^T / dP^T pair, both softmax groups split its columns and hand P^T / dS^T to the MMA
-// warp in 16-column chunks.  Every kernel has one MMA-issuing warp and one TMA-issuing warp.
+// Row kernels: S and dP tiles (128 lanes x 64 columns) are double buffered in tensor memory; the softmax
+// groups turn a buffer into P and dS (16-bit, in place) while the tensor cores work on the other buffer
+// (bwd_row_kernel: one group per buffer; bwd_row2_kernel: both groups split every tile's columns); P and dS
+// then feed the two accumulating MMAs from tensor memory.  Column kernel: one 128-column S^T / dP^T pair,
+// both softmax groups split its columns and hand P^T / dS^T to the MMA warp in 16-column chunks.
 #pragma once
 
 #include <type_traits>
@@ -689,7 +690,8 @@ __device__ __forceinline__ RowItem row_item(const BwdTcParams& P, long it) {
 template <int CW>
 __device__ __forceinline__ void tmem_ld_cw(uint32_t addr, uint32_t (&v)[CW]) {
     if constexpr (CW == 32) ptx::tmem_ld32(addr, v);
-    else ptx::tmem_ld16(addr, v);
+    else if constexpr (CW == 16) ptx::tmem_ld16(addr, v);
+    else ptx::tmem_ld8(addr, v);
     ptx::tmem_wait_ld();
 }
 
@@ -1172,8 +1174,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
     using L = BwdSmem<HD, NS>;
     using namespace ptx;
     using E = El<F16>;
-    constexpr int CW = 16;                                // epilogue chunk width
-    constexpr int NPH = HD / CW;                          // epilogue phases
+    constexpr int CW = HD / 8;                            // epilogue chunk width: four chunks per half of the columns
     static_assert(DWL >= 4 && DWL <= 6, "16, 32 or 64 delta slots per query");
     constexpr int DW = 1 << DWL, QPT = 128 >> DWL;        // delta slots per query, queries per 128-row unit
     constexpr bool TWO_Q = DWL == 4;                      // a warp holds two queries of 16 deltas each
@@ -1427,8 +1428,13 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                 for (int ph = 0; ph < NPHG; ++ph) {
                     const int c = ((wq + ph) & 3) * CW;
                     uint32_t g[CW], u[CW];
-                    tmem_ld16(tm_g + lane_addr + cbase + c, g);
-                    tmem_ld16(tm_u + lane_addr + cbase + c, u);
+                    if constexpr (CW == 16) {
+                        tmem_ld16(tm_g + lane_addr + cbase + c, g);
+                        tmem_ld16(tm_u + lane_addr + cbase + c, u);
+                    } else {
+                        tmem_ld8(tm_g + lane_addr + cbase + c, g);
+                        tmem_ld8(tm_u + lane_addr + cbase + c, u);
+                    }
                     tmem_wait_ld();
 #pragma unroll
                     for (int e = 0; e < CW / 2; ++e) {
@@ -1496,8 +1502,8 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                         } else {
                             // each half warp holds the 16 deltas of one query
                             const int qh = wq * 2 + (lane >> 4);
-                            const float tot = half_warp_transpose_reduce16(v, lane) * p.scale;
-                            if (i0 + qh < p.N) E::st(&dq_out[(long)qh * p.dq.n + c + (lane & 15)], tot);
+                            const float tot = half_warp_transpose_reduce<CW>(v, lane) * p.scale;
+                            if ((lane & 15) < CW && i0 + qh < p.N) E::st(&dq_out[(long)qh * p.dq.n + c + (lane & 15)], tot);
                         }
                     }
 #pragma unroll
@@ -1541,11 +1547,13 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                                                    : ws_head + ((bh * P.num_runs + ri.run) * (p.w2 - 1) + (kbf - (own0 - (p.w2 - 1)))) * HD;
                         float* src = ring + ring_index<HD>(fslot, 0);
                         const int d = cbase + (lane & 15) * 4;
-                        *(float4*)(dst + d) = make_float4(src[d] * mult, src[d + 1] * mult, src[d + 2] * mult, src[d + 3] * mult);
-                        src[d] = 0.f;
-                        src[d + 1] = 0.f;
-                        src[d + 2] = 0.f;
-                        src[d + 3] = 0.f;
+                        if ((lane & 15) * 4 < HALF) {
+                            *(float4*)(dst + d) = make_float4(src[d] * mult, src[d + 1] * mult, src[d + 2] * mult, src[d + 3] * mult);
+                            src[d] = 0.f;
+                            src[d + 1] = 0.f;
+                            src[d + 2] = 0.f;
+                            src[d + 3] = 0.f;
+                        }
                     }
                     flush_lo = max(flush_lo, f_hi);
                     named_barrier_sync(3 + grp, 128);     // cleared slots are visible before the next unit's updates
@@ -1864,7 +1872,22 @@ inline int launch_bwd_t(const KParams& k, const void* q, const void* k1, const v
             using L3 = BwdSmem<64, 3>;
             using L2 = BwdSmem<64, 2>;
             const bool fits3 = L3::kRing + 1024 + 2 * ring_want * 66 * 4 <= L3::kMaxDynamic;
-            if (pl.dw_log2 == 4)
+            constexpr int kDqPart = 2048;     // (the kernel places the staging buffers 2048 bytes behind the rings)
+            const int stage5 = 2 * row2_stage_bytes(5, 64), stage4 = 2 * row2_stage_bytes(4, 64);
+            const int ring_bytes = 2 * ring_want * 66 * 4;
+            const bool fits5 = L3::kRing + 1024 + ring_bytes + kDqPart + stage5 <= L3::kMaxDynamic;
+            const bool fits4 = L3::kRing + 1024 + ring_bytes + kDqPart + stage4 <= L3::kMaxDynamic;
+            const bool fits6 = L3::kRing + 1024 + ring_bytes + kDqPart <= L3::kMaxDynamic;
+            if (pl.dw_log2 == 5 && (fits5 || !need_kv2))     // separate operand / epilogue warpgroups
+                ok = launch_row(has_bias ? bwd_row2_kernel<64, 5, 3, true, F16> : bwd_row2_kernel<64, 5, 3, false, F16>, L3::kRing, L3::kAlloc,
+                                L3::kMaxDynamic, 64, kRow2Threads, kDqPart + stage5);
+            else if (pl.dw_log2 == 4 && (fits4 || !need_kv2))
+                ok = launch_row(has_bias ? bwd_row2_kernel<64, 4, 3, true, F16> : bwd_row2_kernel<64, 4, 3, false, F16>, L3::kRing, L3::kAlloc,
+                                L3::kMaxDynamic, 64, kRow2Threads, kDqPart + stage4);
+            else if (pl.dw_log2 == 6 && (fits6 || !need_kv2))
+                ok = launch_row(has_bias ? bwd_row2_kernel<64, 6, 3, true, F16> : bwd_row2_kernel<64, 6, 3, false, F16>, L3::kRing, L3::kAlloc,
+                                L3::kMaxDynamic, 64, kRow2Threads, kDqPart);
+            else if (pl.dw_log2 == 4)
                 ok = launch_row(has_bias ? bwd_row_kernel<64, 3, true, true, F16> : bwd_row_kernel<64, 3, true, false, F16>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64);
             else
                 ok = (fits3 || !need_kv2) ? launch_row(has_bias ? bwd_row_kernel<64, 3, false, true, F16> : bwd_row_kernel<64, 3, false, false, F16>, L3::kRing, L3::kAlloc, L3::kMaxDynamic, 64)
