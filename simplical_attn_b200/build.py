@@ -4,6 +4,7 @@
 """
 from __future__ import annotations
 
+import concurrent.futures
 import hashlib
 import os
 import subprocess
@@ -60,18 +61,34 @@ def _stale() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile the library if it is missing or was built from other sources; returns its path."""
+    """Compile the library if it is missing or was built from other sources; returns its path.  Every
+    .cu file of csrc/ is one translation unit; the units compile side by side and are then linked."""
     if not force and not _stale():
         return LIB
     nvcc = nvcc_path()
     os.makedirs(LIB_DIR, exist_ok=True)
     digest = source_digest()
-    cmd = [nvcc] + NVCC_FLAGS + ["-o", LIB] + sources()
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or res.returncode != 0:
-        sys.stderr.write(res.stdout + res.stderr)
-    if res.returncode != 0:
+    obj_dir = os.path.join(LIB_DIR, "obj")
+    os.makedirs(obj_dir, exist_ok=True)
+    compile_flags = [f for f in NVCC_FLAGS if f != "-shared"]
+
+    def compile_one(src: str):
+        obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
+        res = subprocess.run([nvcc] + compile_flags + ["-c", "-o", obj, src], capture_output=True, text=True)
+        return obj, res
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=max(1, min(len(sources()), os.cpu_count() or 1))) as pool:
+        results = list(pool.map(compile_one, sources()))
+    for _, res in results:
+        if verbose or res.returncode != 0:
+            sys.stderr.write(res.stdout + res.stderr)
+    if any(res.returncode != 0 for _, res in results):
         raise RuntimeError("nvcc failed building " + LIB)
+    link = subprocess.run([nvcc, "-shared", "-o", LIB] + [obj for obj, _ in results], capture_output=True, text=True)
+    if verbose or link.returncode != 0:
+        sys.stderr.write(link.stdout + link.stderr)
+    if link.returncode != 0:
+        raise RuntimeError("nvcc failed linking " + LIB)
     with open(STAMP, "w") as f:
         f.write(digest + "\n")
     return LIB

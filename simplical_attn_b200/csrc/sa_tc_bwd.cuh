@@ -1768,7 +1768,7 @@ typedef bool (*MakeMapFn)(CUtensorMap*, const void*, int, int, int, int, const s
 // Returns an sa_status, or -1 when the tensor-core backward does not cover the problem.  F16: the tensors are
 // IEEE half instead of bf16.
 template <bool F16>
-inline int launch_bwd_t(const KParams& k, const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
+int launch_bwd_t(const KParams& k, const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
                       const void* o, const float* lse, const void* d_o, void* dq, void* dk1, void* dk2, void* dv1,
                       void* dv2, uint8_t* workspace, DeviceStatus* status, cudaStream_t st, int* nlaunch, MakeMapFn make_map,
                       int sm_count, uint64_t wait_limit_ns) {
@@ -1903,6 +1903,18 @@ inline int launch_bwd_t(const KParams& k, const void* q, const void* k1, const v
     }
     return cudaGetLastError() == cudaSuccess ? SA_OK : SA_ERR_LAUNCH;
 }
+
+// The two element types are compiled in translation units of their own (sa_tc_bwd_bf16.cu, sa_tc_bwd_f16.cu: the
+// kernels of one type take minutes to compile, and the units build side by side); everywhere else the
+// instantiations are only declared.
+#ifndef SA_TC_BWD_INSTANTIATE
+extern template int launch_bwd_t<false>(const KParams&, const void*, const void*, const void*, const void*, const void*, const void*,
+                                        const float*, const void*, void*, void*, void*, void*, void*, uint8_t*, DeviceStatus*,
+                                        cudaStream_t, int*, MakeMapFn, int, uint64_t);
+extern template int launch_bwd_t<true>(const KParams&, const void*, const void*, const void*, const void*, const void*, const void*,
+                                       const float*, const void*, void*, void*, void*, void*, void*, uint8_t*, DeviceStatus*,
+                                       cudaStream_t, int*, MakeMapFn, int, uint64_t);
+#endif
 
 inline int launch_bwd(const KParams& k, const void* q, const void* k1, const void* k2, const void* v1, const void* v2,
                       const void* o, const float* lse, const void* d_o, void* dq, void* dk1, void* dk2, void* dv1,
