@@ -46,7 +46,7 @@ LONG_SEQUENCE = dict(B=1, H=16, Hkv=16, N=65536, D=128, w1=1024, w2=64)     # sp
 # DRAM bytes per launch of each big kernel for ONE batch element of WORKLOAD (dram__bytes_read.sum +
 # dram__bytes_write.sum of the ncu captures summarised under profiles/), and the library version those
 # captures were taken with: the figures are only reported while the library still has that version.
-TRAFFIC = dict(lib_version=200, fwd_tc_kernel=195.1e6, bwd_col_kernel=247.7e6, bwd_row_kernel=397.2e6)
+TRAFFIC = dict(lib_version=200, fwd_tc_kernel=193.6e6, bwd_col_kernel=249.1e6, bwd_row_kernel=396.3e6)
 FALLBACK_PEAKS = dict(bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, hbm_gbs=6650.0)
 
 
