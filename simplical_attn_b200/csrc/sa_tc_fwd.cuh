@@ -431,7 +431,43 @@ fwd_tc_kernel(const __grid_constant__ FwdTcParams P, const __grid_constant__ CUt
                 mbar_wait(&o_ready[r], nu & 1, wctx, 9);
                 if (warp == 8) SA_TR(2, 64 + r);
                 tc_fence_after();
-                if (P.dw_log2 >= 5) {
+                if constexpr (DWL == 4) {
+                    // a warp holds the 16 deltas of two queries, one per half warp: sum them by a register exchange
+                    // within each half, 16 columns at a time; lane L ends up with column (L % 16) of its half's query
+                    uint32_t v[16], cur[8];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) cur[e] = vw[e];
+                    tmem_ld16(t_addr, v);
+                    __nv_bfloat16* orow = o + ug.b * p.o.b + (long)min(i, p.N - 1) * p.o.n + ug.h * p.o.h;
+#pragma unroll
+                    for (int ch = 0; ch < HD / 16; ++ch) {
+                        uint32_t vn[8];                           // the next chunk's V2 values are in flight under this one's reduction
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) vn[e] = 0u;
+                        if (ch + 1 < HD / 16 && row_valid) load_bf16_words<16>(v2row + 16 * (ch + 1), vn);
+                        tmem_wait_ld();
+                        if (ch == HD / 16 - 1) {                  // T has been read: the next unit's first P.V may overwrite it
+                            tc_fence_before();
+                            warp_arrive(&t_free[r]);
+                        }
+                        float y[16];
+#pragma unroll
+                        for (int e = 0; e < 16; e += 2) {
+                            const uint32_t w = cur[e >> 1];
+                            float2 x2 = make_float2(E::lo(w), E::hi(w));
+                            if (BIAS) x2 = __fadd2_rn(x2, make_float2(v2_bias, v2_bias));
+                            const float2 y2 = __fmul2_rn(make_float2(__uint_as_float(v[e]), __uint_as_float(v[e + 1])),
+                                                         __fmul2_rn(x2, make_float2(wrow, wrow)));
+                            y[e] = y2.x;
+                            y[e + 1] = y2.y;
+                        }
+                        if (ch + 1 < HD / 16) tmem_ld16(t_addr + 16 * (ch + 1), v);
+                        const float tot = half_warp_transpose_reduce<16>(y, lane);
+                        if (i < p.N) E::st(&orow[16 * ch + (lane & 15)], tot);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) cur[e] = vn[e];
+                    }
+                } else if (DWL >= 5 || P.dw_log2 >= 5) {
                     // a warp holds 32 consecutive deltas of one query: sum them by a register exchange;
                     // lane L ends up with column L of each 32-column chunk
                     const int wq = row >> 5;                      // warp within the group
