@@ -120,7 +120,17 @@ size_t sa_backward_workspace_size(const sa_params* p);
  * counterpart: its failures surface as Triton exceptions. */
 int sa_read_status(void* workspace, void* stream);
 
-/* The same, also returning where the wait gave up: `where` receives the id of the wait site inside
+/* Reads the status word without synchronising anything: copies it (16 bytes) from `workspace` to
+ * `device_slot` on `stream`, and from there to `host_slot` (pinned host memory) on `side_stream`, which
+ * waits for the first copy through `ev_ready`; `ev_done` is recorded behind the second copy.  Once
+ * `ev_done` has completed, `host_slot` holds {code, wait site, block, 0} as four ints.  The workspace
+ * is free for reuse as soon as `stream` has passed the first copy, and `stream` never waits for the
+ * transfer to the host.  Streams, events and both slots are the caller's.  No counterpart in the
+ * reference. */
+int sa_status_relay(const void* workspace, void* device_slot, void* host_slot, void* stream, void* side_stream,
+                    void* ev_ready, void* ev_done);
+
+/* sa_read_status(), also returning where the wait gave up: `where` receives the id of the wait site inside
  * the kernel and `block` the index of the thread block that recorded it (either may be NULL). */
 int sa_read_status_ex(void* workspace, void* stream, int* where, int* block);
 

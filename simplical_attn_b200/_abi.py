@@ -72,6 +72,8 @@ def load():
     lib.sa_read_status.restype = ctypes.c_int
     lib.sa_read_status_ex.argtypes = [vp, vp, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
     lib.sa_read_status_ex.restype = ctypes.c_int
+    lib.sa_status_relay.argtypes = [vp] * 7
+    lib.sa_status_relay.restype = ctypes.c_int
     lib.sa_read_status_static.argtypes = [vp]
     lib.sa_read_status_static.restype = ctypes.c_int
     lib.sa_set_wait_limit_ns.argtypes = [ctypes.c_uint64]

@@ -490,6 +490,18 @@ int sa_read_status_ex(void* workspace, void* stream, int* where, int* block) {
 
 int sa_read_status(void* workspace, void* stream) { return sa_read_status_ex(workspace, stream, nullptr, nullptr); }
 
+int sa_status_relay(const void* workspace, void* device_slot, void* host_slot, void* stream, void* side_stream, void* ev_ready,
+                    void* ev_done) {
+    if (!workspace || !device_slot || !host_slot || !ev_ready || !ev_done) return SA_ERR_NULL_POINTER;
+    cudaStream_t st = static_cast<cudaStream_t>(stream), side = static_cast<cudaStream_t>(side_stream);
+    cudaEvent_t ready = static_cast<cudaEvent_t>(ev_ready), done = static_cast<cudaEvent_t>(ev_done);
+    const bool ok = cudaMemcpyAsync(device_slot, workspace, sizeof(sa::DeviceStatus), cudaMemcpyDeviceToDevice, st) == cudaSuccess &&
+                    cudaEventRecord(ready, st) == cudaSuccess && cudaStreamWaitEvent(side, ready, 0) == cudaSuccess &&
+                    cudaMemcpyAsync(host_slot, device_slot, sizeof(sa::DeviceStatus), cudaMemcpyDeviceToHost, side) == cudaSuccess &&
+                    cudaEventRecord(done, side) == cudaSuccess;
+    return ok ? SA_OK : SA_ERR_LAUNCH;
+}
+
 int sa_read_status_static(void* stream) {
     void* scratch = static_scratch();
     if (!scratch) return SA_ERR_LAUNCH;

@@ -94,48 +94,56 @@ class _StatusWatch:
     SLOTS = 32                      # pinned status slots per device, reused
 
     def __init__(self):
-        self._dev = {}              # device index -> (pinned [SLOTS, 4] int32, free slots, pending, stream, device [SLOTS, 4] int32)
+        self._dev = {}              # device index -> (view of the pinned [SLOTS, 4] int32 slots, free slots, pending, stream, ...)
 
     def _state(self, index: int):
         st = self._dev.get(index)
         if st is None:
             dev = torch.device("cuda", index)
-            st = (torch.zeros(self.SLOTS, 4, dtype=torch.int32).pin_memory(), list(range(self.SLOTS)), [],
-                  torch.cuda.Stream(dev), torch.empty(self.SLOTS, 4, dtype=torch.int32, device=dev))
+            side = torch.cuda.Stream(dev)
+            host = torch.zeros(self.SLOTS, 4, dtype=torch.int32).pin_memory()
+            small = torch.empty(self.SLOTS, 4, dtype=torch.int32, device=dev)
+            events = []
+            for _ in range(self.SLOTS):                # created once, reused: (workspace copy done, host copy done)
+                pair = (torch.cuda.Event(), torch.cuda.Event())
+                for ev in pair:
+                    ev.record(side)                    # a torch event gets its CUDA handle at its first record
+                events.append(pair)
+            st = (host.numpy(), list(range(self.SLOTS)), [], side, small, events, host.data_ptr(), small.data_ptr(),
+                  side.cuda_stream, host)
             self._dev[index] = st
         return st
 
-    def watch(self, ws: torch.Tensor, label: str) -> None:
-        host, free, pending, side, small = self._state(ws.device.index)
+    def watch(self, ws: torch.Tensor, label: str, stream_handle=None) -> None:
+        _, free, pending, side, small, events, host_ptr, small_ptr, side_handle, _ = self._state(ws.device.index)
         if not free:
             self.poll(ws.device, wait_oldest=True)
         i = free.pop()
         # The status word first goes to a small device slot, on the caller's stream (16 bytes, device to device),
         # so that the workspace itself is not held any longer than the kernels need it.  The device-to-host copy
         # then runs on a stream of its own: on the caller's stream it would queue behind whatever large transfers
-        # keep the copy engines busy and hold the caller's next kernels back.
-        cur = torch.cuda.current_stream(ws.device)
-        small[i].copy_(ws[:16].view(torch.int32))
-        side.wait_stream(cur)
-        with torch.cuda.stream(side):
-            host[i].copy_(small[i], non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record(side)
-        pending.append((ev, i, label))
+        # keep the copy engines busy and hold the caller's next kernels back.  One library call does all of it
+        # (a handful of Python-level stream and event operations would cost more than a small problem's kernels).
+        if stream_handle is None:
+            stream_handle = torch.cuda.current_stream(ws.device).cuda_stream
+        ready, done = events[i]
+        rc = _abi.load().sa_status_relay(ws.data_ptr(), small_ptr + 16 * i, host_ptr + 16 * i, stream_handle, side_handle,
+                                         ready.cuda_event, done.cuda_event)
+        _abi.check("sa_status_relay", rc)
+        pending.append((done, i, label))
 
     def poll(self, device: torch.device, wait: bool = False, wait_oldest: bool = False) -> None:
         if device.index not in self._dev:
             return
-        host, free, pending, _, _ = self._state(device.index)
+        host, free, pending = self._state(device.index)[:3]
         bad = None
         keep = []
         for n, (ev, i, label) in enumerate(pending):
             if wait or (wait_oldest and n == 0):
                 ev.synchronize()
             if ev.query():
-                code, where, block = (int(x) for x in host[i][:3])
-                if code != 0 and bad is None:
-                    bad = (label, code, where, block)
+                if host[i, 0] != 0 and bad is None:          # (a numpy view of the pinned slots: cheap to read)
+                    bad = (label, int(host[i, 0]), int(host[i, 1]), int(host[i, 2]))
                 free.append(i)
             else:
                 keep.append((ev, i, label))
@@ -175,13 +183,14 @@ def two_simplicial_attn_fwd_kernel(q, k1, k2, v1, v2, w1, w2, scale, k2_bias=0.0
     lse = torch.empty((B, H, N), device=q.device, dtype=torch.float32)
     p = _make_params(q, k1, k2, v1, v2, o, w1, w2, scale, k2_bias, v2_bias, halo1, halo2, algo or default_algo)
     ws = _workspace(lib.sa_forward_workspace_size(ctypes.byref(p)), q.device)
+    sh = torch.cuda.current_stream().cuda_stream
     rc = lib.sa_forward(ctypes.byref(p), _ptr(q), _ptr(k1), _ptr(k2), _ptr(v1), _ptr(v2), _ptr(o), _ptr(lse), _ptr(ws),
-                        ws.numel(), _stream())
+                        ws.numel(), ctypes.c_void_p(sh))
     _abi.check("sa_forward", rc)
     if debug_device_status:
-        _abi.check("sa_forward (device)", lib.sa_read_status(_ptr(ws), _stream()))
+        _abi.check("sa_forward (device)", lib.sa_read_status(_ptr(ws), ctypes.c_void_p(sh)))
     else:
-        _status_watch.watch(ws, "sa_forward")
+        _status_watch.watch(ws, "sa_forward", sh)
     return o, lse
 
 
@@ -199,13 +208,14 @@ def two_simplicial_attn_bwd(q, k1, k2, v1, v2, o, lse, d_o, w1, w2, scale, k2_bi
     p.d_o = _strides(d_o)
     p.dq, p.dk1, p.dk2, p.dv1, p.dv2 = (_strides(g) for g in grads)
     ws = _workspace(lib.sa_backward_workspace_size(ctypes.byref(p)), q.device)
+    sh = torch.cuda.current_stream().cuda_stream
     rc = lib.sa_backward(ctypes.byref(p), _ptr(q), _ptr(k1), _ptr(k2), _ptr(v1), _ptr(v2), _ptr(o), _ptr(lse), _ptr(d_o),
-                         *[_ptr(g) for g in grads], _ptr(ws), ws.numel(), _stream())
+                         *[_ptr(g) for g in grads], _ptr(ws), ws.numel(), ctypes.c_void_p(sh))
     _abi.check("sa_backward", rc)
     if debug_device_status:
-        _abi.check("sa_backward (device)", lib.sa_read_status(_ptr(ws), _stream()))
+        _abi.check("sa_backward (device)", lib.sa_read_status(_ptr(ws), ctypes.c_void_p(sh)))
     else:
-        _status_watch.watch(ws, "sa_backward")
+        _status_watch.watch(ws, "sa_backward", sh)
     return tuple(grads)
 
 
