@@ -526,7 +526,9 @@ __device__ __forceinline__ void load_product_tile_shared(uint4* regs, int t, int
         const int w = pr + k * S::RPP;
         const int kb = kb_first + w;
         regs[S::NQ + k] = make_uint4(0, 0, 0, 0);
-        if (w < S::NWIN && kb >= 0) regs[S::NQ + k] = __ldg((const uint4*)(y + (int64_t)kb * ys) + c);
+        // (rows past the end belong to queries past the end of the last tile: they must not be read, and a
+        // zero row keeps the product with the zero query row an exact zero whatever lies behind the tensor)
+        if (w < S::NWIN && kb >= 0 && kb < n_q + halo2) regs[S::NQ + k] = __ldg((const uint4*)(y + (int64_t)kb * ys) + c);
     }
 }
 

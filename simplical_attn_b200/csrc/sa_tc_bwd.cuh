@@ -782,7 +782,7 @@ bwd_row_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ CU
                 const int i = i0 + qq;
                 const int kb = i + p.halo2 - dlt;
                 const bool row_valid = (i < p.N) && (dlt < p.w2) && (kb >= 0);
-                const int ic = min(i, p.N - 1), kc = max(kb, 0);
+                const int ic = min(i, p.N - 1), kc = min(max(kb, 0), p.n2 - 1);      // rows that exist (queries past the end are not stored)
                 const __nv_bfloat16* q_row = q + ri.b * p.q.b + (long)ic * p.q.n + ri.h * p.q.h;
                 const __nv_bfloat16* do_row = d_o + ri.b * p.d_o.b + (long)ic * p.d_o.n + ri.h * p.d_o.h;
                 const __nv_bfloat16* k2_row = k2 + ri.b * p.k2.b + (long)kc * p.k2.n + ri.hk * p.k2.h;
@@ -1397,7 +1397,7 @@ bwd_row2_kernel(const __grid_constant__ BwdTcParams P, const __grid_constant__ C
                 const int i = i0 + qq;
                 const int kb = i + p.halo2 - dlt;
                 const bool row_valid = (i < p.N) && (dlt < p.w2) && (kb >= 0);
-                const int ic = min(i, p.N - 1), kc = max(kb, 0);
+                const int ic = min(i, p.N - 1), kc = min(max(kb, 0), p.n2 - 1);      // rows that exist (queries past the end are not stored)
                 const __nv_bfloat16* q_row = q + ri.b * p.q.b + (long)ic * p.q.n + ri.h * p.q.h + cbase;
                 const __nv_bfloat16* do_row = d_o + ri.b * p.d_o.b + (long)ic * p.d_o.n + ri.h * p.d_o.h + cbase;
                 const __nv_bfloat16* k2_row = k2 + ri.b * p.k2.b + (long)kc * p.k2.n + ri.hk * p.k2.h + cbase;

@@ -88,6 +88,8 @@ ORACLE_CASES = [
     (1, 130, 2, 2, 128, 300, 128, 0.0, 0.0, 0, 0),     # widest K2 window: one query per row tile
     (1, 210, 2, 1, 64, 70, 14, 0.05, 0.0, 0, 0),       # D = 64 with 16 delta slots, two of them masked
     (1, 300, 2, 2, 64, 90, 50, 0.0, 0.1, 0, 0),        # D = 64 with 64 delta slots
+    (1, 333, 4, 2, 64, 100, 32, 0.0, 0.0, 0, 0),       # D = 64 with 32 delta slots, grouped heads
+    (1, 200, 2, 2, 64, 70, 24, 0.1, 0.0, 69, 23),      # D = 64, 32 delta slots (8 masked), bias, halo rows
 ]
 
 
@@ -133,6 +135,35 @@ def test_wide_k2_window_vs_cpu_oracle(case, dtype):
     assert float((lse.cpu() - ref[1]).abs().max()) <= 2e-2
     for nm, g, r in zip(("dq", "dk1", "dk2", "dv1", "dv2"), grads, ref[2:]):
         assert _grad_err(g, r) <= TOL_G_BF16, nm
+
+
+@pytest.mark.parametrize("shape", [(260, 128, 130, 16), (300, 128, 100, 32), (150, 128, 40, 64), (210, 64, 70, 14), (333, 64, 100, 32),
+                                   (130, 128, 300, 128), (330, 128, 40, 160)])
+def test_nothing_behind_the_tensors_is_read_into_the_results(shape):
+    """The last 128-row tile of a sequence has rows for queries past the end; their K2 / V2 window rows lie
+    past the end of K2 / V2.  Whatever is in memory there (here: NaN, the tensors are views of larger buffers)
+    must not reach any result."""
+    N, D, w1, w2 = shape
+    B, H, Hkv = 1, 2, 2
+    q, k1, k2, v1, v2, do = so.make_inputs(B, N, H, Hkv, D, seed=21, seed_do=22)
+    scale = 1.0 / math.sqrt(D)
+
+    def padded(t):
+        big = torch.full((B, N + 192, t.shape[2], D), float("nan"), dtype=torch.bfloat16, device=DEV)
+        big[:, :N] = t.to(DEV).to(torch.bfloat16)
+        return big[:, :N]
+
+    clean = [t.to(DEV).to(torch.bfloat16) for t in (q, k1, k2, v1, v2, do)]
+    dirty = [padded(t) for t in (q, k1, k2, v1, v2, do)]
+    outs = []
+    for ts in (clean, dirty):
+        o, lse = sab.two_simplicial_attn_fwd_kernel(*ts[:5], w1, w2, scale, algo="tcgen05")
+        grads = sab.two_simplicial_attn_bwd(*ts[:5], o, lse, ts[5], w1, w2, scale, algo="tcgen05")
+        outs.append((o, lse) + tuple(grads))
+    torch.cuda.synchronize()
+    for nm, a, b in zip(("o", "lse", "dq", "dk1", "dk2", "dv1", "dv2"), *outs):
+        assert bool(torch.isfinite(b.float()).all()), nm
+        assert torch.equal(a, b), nm
 
 
 def test_tensor_core_vs_general_medium():
@@ -296,11 +327,13 @@ def test_window_sweep_tensor_core_vs_general(w1, w2):
         assert so.rel_l2(a.float().cpu(), b.float().cpu()) <= TOL_G_BF16, nm
 
 
-@pytest.mark.parametrize("w2", [16, 32, 64])
+@pytest.mark.parametrize("w2", [16, 32, 64, 128, 200])
 def test_partial_gradient_requests_match_full_call(w2):
     """The reference's two backward kernels are separate calls (dQ/dK1/dV1 and dK2/dV2).  Asking the
-    tensor-core path for a subset must give exactly the tensors of the full call (w2 = 32 runs the row
-    kernel with separate epilogue warpgroups, 16 and 64 the other one) and None for the rest."""
+    tensor-core path for a subset must give the tensors of the full call and None for the rest: exactly
+    with 16, 32 and 64 K2 positions (the row kernel with operand / epilogue warpgroups), and to the last
+    bit or two of the 16-bit results with 128 (the other row kernel sums dQ in another order when it
+    keeps no dK2 / dV2 ring) and 200 (two passes over chunks of the K2 window)."""
     B, N, H, Hkv, D, w1 = 1, 700, 4, 2, 128, 200
     q, k1, k2, v1, v2, do = so.make_inputs(B, N, H, Hkv, D, seed=11 + w2)
     cfg = dict(w1=w1, w2=w2, scale=1.0 / math.sqrt(D), k2_bias=0.0, v2_bias=0.0)
@@ -310,8 +343,10 @@ def test_partial_gradient_requests_match_full_call(w2):
                  (False, False, False, False, True)):
         _, _, part = _run(ins, cfg, "tcgen05", need=need)
         for nm, n, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), need, part, full):
-            if n:
+            if n and w2 <= 64:
                 assert torch.equal(a, b), (nm, need)
+            elif n:
+                assert so.rel_l2(a.float().cpu(), b.float().cpu()) <= 2e-3, (nm, need)
             else:
                 assert a is None, (nm, need)
 
