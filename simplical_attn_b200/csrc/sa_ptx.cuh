@@ -60,6 +60,8 @@ struct WaitCtx {
 
 #ifdef SA_TRACE
 // Trace builds only: block 0 records (clock, event) pairs per role; read back through sa_trace_read.
+// (The buffers exist once per translation unit: build sa_api.cu alone with -DSA_TRACE
+// -DSA_TC_BWD_INSTANTIATE, which instantiates the backward there too.  The same holds for -DSA_PROFILE.)
 // The event counter of a role lives in a register of the recording warp (SA_TR_DECL in the scope of
 // the role's code), so that recording costs one store and no load.
 __device__ unsigned long long g_trace[16][2048];
