@@ -167,6 +167,31 @@ def test_nothing_behind_the_tensors_is_read_into_the_results(shape, algo):
         assert torch.equal(a, b), nm
 
 
+@pytest.mark.parametrize("shape", [(1, 700, 4, 2, 128, 200, 32, 0, 0), (2, 260, 2, 2, 128, 130, 16, 0, 0), (1, 150, 2, 1, 128, 40, 64, 0, 0),
+                                   (1, 130, 2, 2, 128, 300, 128, 0, 0), (1, 330, 2, 2, 128, 40, 160, 0, 0), (1, 333, 4, 2, 64, 100, 32, 0, 0),
+                                   (1, 96, 2, 1, 128, 48, 12, 47, 11)])
+def test_workspace_contents_do_not_matter(shape, monkeypatch):
+    """The kernels write every partial sum of the workspace before they read it: a workspace full of NaN
+    bit patterns (behind the status word, which must start at zero) gives the same results, bit for bit."""
+    B, N, H, Hkv, D, w1, w2, h1, h2 = shape
+    q, k1, k2, v1, v2, do = so.make_inputs(B, N, H, Hkv, D, seed=31, seed_do=32, halo1=h1, halo2=h2)
+    cfg = dict(w1=w1, w2=w2, scale=1.0 / math.sqrt(D), k2_bias=0.0, v2_bias=0.0)
+    ins = dict(q=q, k1=k1, k2=k2, v1=v1, v2=v2, do=do)
+    clean = _run(ins, cfg, "tcgen05", halo1=h1, halo2=h2)
+
+    def nan_workspace(nbytes, device):
+        ws = torch.full((max(int(nbytes), 256),), 0xFF, dtype=torch.uint8, device=device)
+        ws[:256].zero_()
+        return ws
+
+    monkeypatch.setattr(host, "_workspace", nan_workspace)
+    dirty = _run(ins, cfg, "tcgen05", halo1=h1, halo2=h2)
+    for nm, a, b in zip(("o", "lse"), clean[:2], dirty[:2]):
+        assert torch.equal(a, b), nm
+    for nm, a, b in zip(("dq", "dk1", "dk2", "dv1", "dv2"), clean[2], dirty[2]):
+        assert bool(torch.isfinite(b.float()).all()) and torch.equal(a, b), nm
+
+
 def test_tensor_core_vs_general_medium():
     """Same bf16 inputs through both kernel families at a size the CPU oracle would take minutes for."""
     B, N, H, Hkv, D, w1, w2 = 1, 2048, 4, 2, 128, 512, 32
