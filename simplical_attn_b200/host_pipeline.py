@@ -47,7 +47,7 @@ def local_cpus(device) -> Optional[set]:
         with open(path) as f:
             cpus = _cpu_list(f.read())
         return cpus or None
-    except (OSError, AttributeError, ValueError):
+    except (OSError, AttributeError, ValueError, RuntimeError, AssertionError):
         return None
 
 

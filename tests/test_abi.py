@@ -104,3 +104,23 @@ def test_host_pipeline_chunk_plan():
         ch = plan_chunks(B, Hkv)
         assert sorted(ch) == ch and all(h1 > h0 for _, h0, h1 in ch)
         assert sum(h1 - h0 for _, h0, h1 in ch) == B * Hkv
+
+
+def test_cpu_list_parsing_and_numa_helper_without_a_gpu():
+    from simplical_attn_b200 import host_pipeline as hp
+    assert hp._cpu_list("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert hp._cpu_list("") == set()
+    assert hp.local_cpus("cuda:0") is None or isinstance(hp.local_cpus("cuda:0"), set)      # no GPU here: None
+    with hp.near("cuda:0") as took_effect:                                                   # must be harmless
+        assert took_effect in (False, True)
+
+
+def test_library_staleness_follows_source_contents(tmp_path, monkeypatch):
+    """The library counts as current exactly while the digest recorded at build time matches the sources,
+    whatever the file times say."""
+    from simplical_attn_b200 import build as b
+    assert not b._stale()                                   # built by the session fixture / build step
+    digest = b.source_digest()
+    assert open(b.STAMP).read().strip() == digest
+    monkeypatch.setattr(b, "NVCC_FLAGS", b.NVCC_FLAGS + ["-DSOMETHING_ELSE"])
+    assert b.source_digest() != digest and b._stale()       # other flags (or sources): stale
